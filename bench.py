@@ -1,0 +1,406 @@
+#!/usr/bin/env python
+"""Benchmark of the FP8 GEMM path: the DeepSeek-V3 Linear shape sweep (BASELINE config 2).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One step = one pass of fp8_gemm over every (shape, M) pair of the sweep, M-major so that
+540 MB of other weights stream between two uses of any weight (inputs larger than L2).
+`value`  : aggregate fp8_gemm TFLOP/s with FP8 activations, weights and scales resident in HBM.
+`e2e`    : the same sweep through the drop-in module (`kernel.act_quant` + `kernel.fp8_gemm`) with the
+           bf16 activations in pinned host memory and the bf16 results read back to the host, every step.
+`roofline`: the tcgen05 token-major kernel (launches with M >= 256), flops / CUDA-event time per launch.
+`cpu_baseline` / `--impl reference`: the CPU restatement of the reference's kernel.py (oracle/) on the
+           host cores, on a bounded sample of the sweep (the M = 64 column).
+
+N > 1: every rank holds the TP=N shard of each Linear (column-parallel N/ws, row-parallel K/ws followed
+by an NCCL all_reduce of the partial output, as model.py:262-264 does); total work is fixed (strong scaling).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "deepseek-v3_b200")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+MS = [1, 8, 32, 64, 256, 1024, 4096, 16384]
+# name, K (in), N (out), parallel kind under tensor parallelism (model.py:208-267)
+BASE_SHAPES = [
+    ("wq_a", 7168, 1536, "replicated"),
+    ("wq_b", 1536, 24576, "column"),
+    ("wkv_a", 7168, 576, "replicated"),
+    ("wkv_b", 512, 32768, "column"),
+    ("wo", 16384, 7168, "row"),
+    ("dense_w13", 7168, 18432, "column"),
+    ("dense_w2", 18432, 7168, "row"),
+    ("expert_w13", 7168, 2048, "replicated"),   # routed experts are never TP-sliced
+    ("expert_w2", 2048, 7168, "replicated"),
+]
+SHARED = [("shared_w13", 7168, 2048, "column"), ("shared_w2", 2048, 7168, "row")]
+
+
+def shard(shape, tp):
+    name, K, N, kind = shape
+    if kind == "column":
+        return (f"{name}/tp{tp}", K, N // tp, kind)
+    if kind == "row":
+        return (f"{name}/tp{tp}", K // tp, N, kind)
+    return shape
+
+
+def sweep_rows(world: int):
+    """Per-rank list of (name, K, N, kind, needs_all_reduce)."""
+    if world == 1:
+        rows = [(n, k, o, kind, False) for n, k, o, kind in BASE_SHAPES]
+        rows += [(*shard(s, 8), False) for s in BASE_SHAPES + SHARED if s[3] != "replicated"]
+        return rows
+    rows = []
+    for s in BASE_SHAPES + SHARED:
+        n, k, o, kind = shard(s, world)
+        rows.append((n, k, o, kind, kind == "row"))
+    return rows
+
+
+def gemm_flops(M, N, K):
+    return 2.0 * M * N * K
+
+
+def gemm_bytes(M, N, K):
+    kc = -(-K // 128)
+    return M * K + N * K + 4 * M * kc + 4 * (-(-N // 128)) * kc + 2 * M * N
+
+
+def read_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while a region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.lines, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.t.join(timeout=5)
+        sm, mx, pw, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0])); mx.append(float(f[1])); pw.append(float(f[2]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        # "under load": the upper half of the samples by clock excludes idle gaps around the region
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(pw) if pw else None, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------------------
+# reference arm / CPU baseline: the oracle port on the host cores
+# --------------------------------------------------------------------------------------
+
+def cpu_sample_inputs(rows, M, seed=0):
+    import torch
+    from oracle import oracle as O
+    g = torch.Generator().manual_seed(seed)
+    cases = []
+    for name, K, N, _, _ in rows:
+        w = (torch.randn(N, K, generator=g) * 0.02).to(torch.bfloat16)
+        wq, ws = O.weight_quant(w)
+        x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+        cases.append((name, x, wq, ws))
+    return cases
+
+
+def cpu_pass(cases):
+    """act_quant + fp8_gemm on the CPU oracle for every case; returns (seconds, gemm flops)."""
+    from oracle import oracle as O
+    t0 = time.perf_counter()
+    fl = 0.0
+    for _, x, wq, ws in cases:
+        xq, xs = O.act_quant(x)
+        O.fp8_gemm(xq, xs, wq, ws)
+        fl += gemm_flops(x.size(0), wq.size(0), x.size(1))
+    return time.perf_counter() - t0, fl
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import oracle as O
+    rows = sweep_rows(1)
+    M = 64
+    cases = cpu_sample_inputs(rows, M)
+    for _ in range(args.warmup):
+        cpu_pass(cases)
+    t, fl = 0.0, 0.0
+    for _ in range(args.steps):
+        dt, f = cpu_pass(cases)
+        t += dt
+        fl += f
+    val = fl / t / 1e12
+    sample = f"M=64 column of the sweep ({len(rows)} shapes), act_quant+fp8_gemm per shape"
+    line = {
+        "impl": "reference", "metric": "fp8_gemm_tflops_v3_shape_sweep", "value": val, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 x fp8_e4m3 -> fp32",
+        "data": "synthetic", "config": workload_config(1),
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": O.num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+        "note": "reference = CPU restatement of inference/kernel.py (oracle/dsv3_oracle.c, OpenMP); the Python/Triton "
+                "reference itself cannot travel to the GPU box",
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(world):
+    rows = sweep_rows(world)
+    return {
+        "workload": "BASELINE configs[1]: fp8_gemm sweep over DeepSeek-V3 Linear shapes (dim 7168), "
+                    f"{len(rows)} (K->N) rows x M in {MS}; activations N(0,1) bf16 -> act_quant, weights N(0,0.02) "
+                    "quantised per 128x128 block",
+        "shapes": [f"{n}:{k}->{o}" for n, k, o, _, _ in rows],
+        "m_values": MS, "block_size": 128,
+        "parallelism": "single GPU" if world == 1 else f"tp{world}: column N/ws, row K/ws + NCCL all_reduce",
+        "l2": "inputs larger than L2: the sweep runs M-major, so >500 MB of other weights stream between two "
+              "uses of any weight (L2 is 126 MB)",
+    }
+
+
+# --------------------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------------------
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    import dsv3_b200
+    import kernel
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    torch.set_default_dtype(torch.bfloat16)
+    torch.manual_seed(1234 + rank)
+    peaks = read_peaks()
+    rows = sweep_rows(world)
+
+    # ---- synthetic, resident inputs -------------------------------------------------
+    Mmax = max(MS)
+    acts = {}       # K -> (x bf16, xq fp8, xs fp32), all [Mmax, ...]
+    for K in sorted({r[1] for r in rows}):
+        x = torch.randn(Mmax, K, device=dev, dtype=torch.bfloat16)
+        xq, xs = kernel.act_quant(x)
+        acts[K] = (x, xq, xs)
+    weights = {}
+    for name, K, N, _, _ in rows:
+        w = (torch.randn(N, K, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+        weights[name] = dsv3_b200.weight_quant(w)
+        del w
+    plan = [(name, K, N, M, ar) for M in MS for (name, K, N, _, ar) in rows]   # M-major
+    total_flops = sum(gemm_flops(M, N, K) for _, K, N, M, _ in plan)
+
+    def one_step(events=None):
+        for name, K, N, M, ar in plan:
+            _, xq, xs = acts[K]
+            wq, ws = weights[name]
+            if events is not None:
+                e0 = torch.cuda.Event(enable_timing=True); e0.record()
+            y = kernel.fp8_gemm(xq[:M], xs[:M], wq, ws)
+            if events is not None:
+                e1 = torch.cuda.Event(enable_timing=True); e1.record()
+                events.append((name, K, N, M, e0, e1))
+            if ar:
+                dist.all_reduce(y)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        one_step()
+    dsv3_b200.check_device_status()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    # ---- timed region 1: resident inputs ----------------------------------------------
+    events = []
+    barrier()
+    t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(args.steps):
+        one_step(events)
+    t1.record()
+    barrier()
+    ms = t0.elapsed_time(t1)
+    if world > 1:
+        tt = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms = tt.item()
+    dsv3_b200.check_device_status()
+
+    # ---- timed region 2: end to end through the drop-in module, host buffers ----------
+    hx = {K: torch.empty(Mmax, K, dtype=torch.bfloat16, pin_memory=True).copy_(acts[K][0].cpu()) for K in acts}
+    max_out = max(M * N for _, _, N, M, _ in plan)
+    hy = torch.empty(max_out, dtype=torch.bfloat16, pin_memory=True)
+    h2d = sum(M * K * 2 for _, K, _, M, _ in plan)
+    d2h = sum(M * N * 2 for _, _, N, M, _ in plan)
+
+    def e2e_step():
+        for name, K, N, M, ar in plan:
+            wq, ws = weights[name]
+            x = hx[K][:M].to(dev, non_blocking=True)
+            xq, xs = kernel.act_quant(x)
+            y = kernel.fp8_gemm(xq, xs, wq, ws)
+            if ar:
+                dist.all_reduce(y)
+            hy[: M * N].view(M, N).copy_(y, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    s0 = torch.cuda.Event(enable_timing=True); s1 = torch.cuda.Event(enable_timing=True)
+    s0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    s1.record()
+    barrier()
+    ms_e2e = s0.elapsed_time(s1)
+    if world > 1:
+        tt = torch.tensor([ms_e2e], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms_e2e = tt.item()
+    dsv3_b200.check_device_status()
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- per-kernel roofline from the per-launch events of region 1 -------------------
+    big_t = big_f = small_t = small_b = 0.0
+    n_big = n_small = 0
+    per_shape = {}
+    for name, K, N, M, e0, e1 in events:
+        dt = e0.elapsed_time(e1) * 1e-3
+        key = f"{name}@M={M}"
+        acc = per_shape.setdefault(key, [0.0, 0, gemm_flops(M, N, K), gemm_bytes(M, N, K)])
+        acc[0] += dt; acc[1] += 1
+        if M >= 256:
+            big_t += dt; big_f += gemm_flops(M, N, K); n_big += 1
+        elif M <= 64:
+            small_t += dt; small_b += gemm_bytes(M, N, K); n_small += 1
+    fp8_peak = 2.0 * peaks["bf16_tflops_sustained"]
+    roofline = {
+        "kernel": "fp8_gemm_tc_kernel<128,false> (tcgen05, token-major tiles; launches with M >= 256)",
+        "bound": "tensor", "achieved": big_f / big_t / 1e12 if big_t else None, "peak": fp8_peak, "unit": "TFLOP/s",
+        "frac": (big_f / big_t / 1e12) / fp8_peak if big_t else None, "traffic": None,
+        "peak_source": f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({peaks['source']}); FP8 issues at twice the bf16 rate",
+        "launches": n_big, "avg_launch_us": big_t / n_big * 1e6 if n_big else None,
+        "algorithmic": "2*M*N*K flops per launch",
+    }
+    roofline_decode = {
+        "kernel": "fp8_gemm_tc_kernel<BN,true> (tcgen05, weight-major tiles, split-K; launches with M <= 64)",
+        "bound": "hbm", "achieved": small_b / small_t / 1e9 if small_t else None, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+        "frac": (small_b / small_t / 1e9) / peaks["hbm_gbs"] if small_t else None, "traffic": None,
+        "peak_source": f"hbm_gbs of MEASURED_PEAKS.json ({peaks['source']})",
+        "launches": n_small, "algorithmic": "M*K + N*K + scales + 2*M*N bytes per launch",
+    }
+    detail = {k: {"us": v[0] / v[1] * 1e6, "tflops": v[2] / (v[0] / v[1]) / 1e12, "gbs": v[3] / (v[0] / v[1]) / 1e9}
+              for k, v in per_shape.items()}
+
+    if world > 1:
+        dist.barrier()
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    # ---- CPU baseline (rank 0, N=1 only): the oracle on a bounded sample ----------------
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        from oracle import oracle as O
+        cases = cpu_sample_inputs(sweep_rows(1), 64)
+        dt, fl = cpu_pass(cases)
+        cpu = {"value": fl / dt / 1e12, "unit": "TFLOP/s", "cores": O.num_threads(), "kind": "port",
+               "sample": f"M=64 column of the sweep ({len(cases)} shapes), act_quant+fp8_gemm per shape, one pass, {dt:.1f} s"}
+
+    agg = total_flops * world * args.steps / (ms * 1e-3) / 1e12
+    agg_e2e = total_flops * world * args.steps / (ms_e2e * 1e-3) / 1e12
+    line = {
+        "metric": "fp8_gemm_tflops_v3_shape_sweep", "value": agg, "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "fp8_e4m3 x fp8_e4m3 -> fp32", "data": "synthetic", "config": workload_config(world),
+        "roofline": roofline, "roofline_decode": roofline_decode, "cpu_baseline": cpu,
+        "e2e": {"value": agg_e2e, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": ms_e2e / args.steps,
+                "path": "pinned host bf16 activations -> kernel.act_quant -> kernel.fp8_gemm -> bf16 result to pinned host; "
+                        "weights resident on the device"},
+        "gpu_launches": len(plan) * args.steps, "gpu_launches_e2e": 2 * len(plan) * args.steps,
+        "clocks": clocks, "per_shape": detail,
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,137 @@
+// act_quant for sm_100a: per-(1 x block) FP8 e4m3 quantisation of bf16 activations.
+//
+// Replaces inference/kernel.py:9-35 (act_quant_kernel) and its launch at :55-56.
+// The reference runs one 128-thread program per 128-element block with one element
+// per thread; here a half-warp owns a block (16 lanes x 16 bytes), every thread keeps
+// several independent blocks in flight, and the grid is sized from the SM count.
+//
+// Bit-exactness contract (what the reference's kernel computes when compiled for a GPU):
+//   amax = max|x| (NaN operands dropped) ; amax = max(amax, 1e-4f)
+//   s = div.full.f32(amax, 448) ; [ue8m0: s = exp2(ceil(log2(s)))]
+//   y = cvt.rn.satfinite.e4m3(div.full.f32(x, s))
+#include "common.cuh"
+
+namespace dsv3 {
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kUnroll = 4;  // blocks in flight per half-warp per loop trip
+
+__device__ __forceinline__ float scale_from_amax(float amax, int scale_fmt) {
+    amax = fmaxf(amax, 1e-4f);
+    float s = div_full(amax, 448.0f);
+    if (scale_fmt == DSV3_SCALE_FMT_UE8M0) s = exp2f(ceilf(log2f(s)));
+    return s;
+}
+
+__device__ __forceinline__ float amax8(const uint4& v) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    float m = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        m = fmaxf(m, fabsf(bf16_bits_to_float(w[i] & 0xFFFFu)));
+        m = fmaxf(m, fabsf(__uint_as_float(w[i] & 0xFFFF0000u)));
+    }
+    return m;
+}
+
+__device__ __forceinline__ uint2 quant8(const uint4& v, float s) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint16_t p[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float lo = div_full(bf16_bits_to_float(w[i] & 0xFFFFu), s);
+        const float hi = div_full(__uint_as_float(w[i] & 0xFFFF0000u), s);
+        p[i] = cvt_e4m3x2(lo, hi);
+    }
+    return make_uint2(static_cast<uint32_t>(p[0]) | (static_cast<uint32_t>(p[1]) << 16),
+                      static_cast<uint32_t>(p[2]) | (static_cast<uint32_t>(p[3]) << 16));
+}
+
+// block_size == 128.  nblk = rows * K / 128; block b covers elements [128 b, 128 b + 128).
+__global__ void __launch_bounds__(kThreads) act_quant128_kernel(const uint4* __restrict__ x, uint2* __restrict__ y,
+                                                                 float* __restrict__ s, int64_t nblk, int scale_fmt) {
+    const int lane16 = threadIdx.x & 15;
+    const int64_t hw = (static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x) >> 4;  // global half-warp id
+    const int64_t nhw = (static_cast<int64_t>(gridDim.x) * kThreads) >> 4;
+    // both half-warps of a warp run the same number of trips (shuffles need all 32 lanes)
+    const int64_t warp_first = hw & ~static_cast<int64_t>(1);
+    for (int64_t base = warp_first; base < nblk; base += nhw * kUnroll) {
+        const int64_t b0 = base + (hw & 1);
+        uint4 v[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const int64_t b = b0 + u * nhw;
+            v[u] = (b < nblk) ? __ldcs(x + b * 16 + lane16) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const int64_t b = b0 + u * nhw;
+            float m = amax8(v[u]);
+            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
+            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 4));
+            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+            const float sc = scale_from_amax(m, scale_fmt);
+            if (b < nblk) {
+                y[b * 16 + lane16] = quant8(v[u], sc);
+                if (lane16 == 0) s[b] = sc;
+            }
+        }
+    }
+}
+
+// Any block size that is a multiple of 8 and at most 1024: one warp per block.
+__global__ void __launch_bounds__(kThreads) act_quant_generic_kernel(const uint4* __restrict__ x,
+                                                                      uint2* __restrict__ y, float* __restrict__ s,
+                                                                      int64_t nblk, int groups, int scale_fmt) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x) >> 5;
+    const int64_t nwarps = (static_cast<int64_t>(gridDim.x) * kThreads) >> 5;
+    for (int64_t b = warp; b < nblk; b += nwarps) {
+        uint4 v[4];
+        float m = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int g = lane + 32 * i;
+            v[i] = (g < groups) ? x[b * groups + g] : make_uint4(0, 0, 0, 0);
+            m = fmaxf(m, amax8(v[i]));
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        const float sc = scale_from_amax(m, scale_fmt);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int g = lane + 32 * i;
+            if (g < groups) y[b * groups + g] = quant8(v[i], sc);
+        }
+        if (lane == 0) s[b] = sc;
+    }
+}
+
+}  // namespace
+
+int launch_act_quant(const void* x, int64_t rows, int64_t K, int block_size, int scale_fmt, void* y, float* s,
+                     cudaStream_t stream) {
+    const int64_t nblk = rows * (K / block_size);
+    if (nblk == 0) return DSV3_OK;
+    const int64_t cap = static_cast<int64_t>(num_sms()) * 8;  // 8 resident CTAs of 256 threads per SM
+    if (block_size == 128) {
+        const int64_t per_cta = (kThreads / 16) * kUnroll;
+        int64_t grid = (nblk + per_cta - 1) / per_cta;
+        if (grid > cap) grid = cap;
+        act_quant128_kernel<<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
+            static_cast<const uint4*>(x), static_cast<uint2*>(y), s, nblk, scale_fmt);
+    } else {
+        const int64_t per_cta = kThreads / 32;
+        int64_t grid = (nblk + per_cta - 1) / per_cta;
+        if (grid > cap) grid = cap;
+        act_quant_generic_kernel<<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
+            static_cast<const uint4*>(x), static_cast<uint2*>(y), s, nblk, block_size / 8, scale_fmt);
+    }
+    DSV3_CUDA_TRY(cudaGetLastError());
+    return DSV3_OK;
+}
+
+}  // namespace dsv3

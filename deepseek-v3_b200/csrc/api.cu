@@ -1,0 +1,221 @@
+// extern "C" surface of libdsv3_b200.so: argument checks, kernel selection, status plumbing.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "common.cuh"
+
+namespace dsv3 {
+
+// kernels (one translation unit each)
+int launch_act_quant(const void* x, int64_t rows, int64_t K, int block_size, int scale_fmt, void* y, float* s,
+                     cudaStream_t stream);
+int launch_weight_dequant(const void* w, const float* s, int64_t N, int64_t K, int block, void* y, cudaStream_t stream);
+int launch_weight_quant(const void* w, int64_t N, int64_t K, void* q, float* s, cudaStream_t stream);
+int launch_fp8_gemm_simple(const void* a, const float* a_s, const void* b, const float* b_s, int64_t M, int64_t N,
+                           int64_t K, void* c, cudaStream_t stream);
+
+struct TcPlan {
+    bool swap;
+    int bn;
+    int tiles_p, tiles_q, splits, kc;
+};
+bool tc_supported(const void* a, const void* b, const void* c, int64_t M, int64_t N, int64_t K);
+TcPlan tc_plan(int64_t M, int64_t N, int64_t K, int force_kernel, int force_split);
+size_t tc_workspace_bytes(const TcPlan& pl, int64_t M, int64_t N);
+int launch_fp8_gemm_tc(const void* a, const float* a_s, const void* b, const float* b_s, int64_t M, int64_t N,
+                       int64_t K, void* c, void* workspace, size_t workspace_bytes, const TcPlan& pl,
+                       cudaStream_t stream);
+
+// ------------------------------------------------------------------ errors
+static thread_local char t_last_error[512] = "";
+
+void set_last_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(t_last_error, sizeof(t_last_error), fmt, ap);
+    va_end(ap);
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+    set_last_error("%s: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
+    return DSV3_ERR_CUDA;
+}
+
+int num_sms() {
+    static int cached[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+// ------------------------------------------------------------------ status words
+__device__ unsigned int g_status[4];
+
+unsigned int* status_device_ptr() {
+    static unsigned int* cached[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        set_last_error("status word: no current device");
+        return nullptr;
+    }
+    if (!cached[dev]) {
+        void* ptr = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&ptr, g_status);
+        if (e != cudaSuccess) {
+            cuda_fail(e, "cudaGetSymbolAddress(g_status)");
+            return nullptr;
+        }
+        cached[dev] = static_cast<unsigned int*>(ptr);
+    }
+    return cached[dev];
+}
+
+static int g_force_kernel = 0;
+static int g_force_split = 0;
+
+static bool is_null(const void* p) { return p == nullptr; }
+
+}  // namespace dsv3
+
+using namespace dsv3;
+
+extern "C" {
+
+int dsv3_version(void) { return 100; }
+
+const char* dsv3_strerror(int status) {
+    switch (status) {
+        case DSV3_OK: return "ok";
+        case DSV3_ERR_INVALID_ARGUMENT: return "invalid argument";
+        case DSV3_ERR_UNSUPPORTED: return "unsupported shape or option";
+        case DSV3_ERR_CUDA: return "CUDA call failed";
+        case DSV3_ERR_WORKSPACE: return "workspace missing or too small";
+        case DSV3_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait gave up";
+        default: return "unknown status";
+    }
+}
+
+const char* dsv3_last_error(void) { return t_last_error; }
+
+int dsv3_act_quant(const void* x, int64_t rows, int64_t K, int block_size, int scale_fmt, void* y, float* s,
+                   dsv3_stream_t stream) {
+    if (rows < 0 || K < 0 || block_size <= 0) {
+        set_last_error("act_quant: negative size or block_size <= 0");
+        return DSV3_ERR_INVALID_ARGUMENT;
+    }
+    if (K % block_size != 0) {
+        set_last_error("act_quant: last dimension %lld is not divisible by block_size %d", (long long)K, block_size);
+        return DSV3_ERR_INVALID_ARGUMENT;
+    }
+    if (scale_fmt != DSV3_SCALE_FMT_FP32 && scale_fmt != DSV3_SCALE_FMT_UE8M0) {
+        set_last_error("act_quant: unknown scale_fmt %d", scale_fmt);
+        return DSV3_ERR_INVALID_ARGUMENT;
+    }
+    if (rows == 0 || K == 0) return DSV3_OK;
+    if (is_null(x) || is_null(y) || is_null(s)) {
+        set_last_error("act_quant: null pointer");
+        return DSV3_ERR_INVALID_ARGUMENT;
+    }
+    if (block_size % 8 != 0 || block_size > 1024) {
+        set_last_error("act_quant: block_size %d must be a multiple of 8 and at most 1024", block_size);
+        return DSV3_ERR_UNSUPPORTED;
+    }
+    if (reinterpret_cast<uintptr_t>(x) % 16 != 0 || reinterpret_cast<uintptr_t>(y) % 8 != 0) {
+        set_last_error("act_quant: x must be 16-byte and y 8-byte aligned");
+        return DSV3_ERR_UNSUPPORTED;
+    }
+    return launch_act_quant(x, rows, K, block_size, scale_fmt, y, s, static_cast<cudaStream_t>(stream));
+}
+
+int dsv3_weight_dequant(const void* w, const float* s, int64_t N, int64_t K, int block_size, void* y,
+                        dsv3_stream_t stream) {
+    if (N < 0 || K < 0 || block_size <= 0) {
+        set_last_error("weight_dequant: negative size or block_size <= 0");
+        return DSV3_ERR_INVALID_ARGUMENT;
+    }
+    if (N == 0 || K == 0) return DSV3_OK;
+    if (is_null(w) || is_null(s) || is_null(y)) {
+        set_last_error("weight_dequant: null pointer");
+        return DSV3_ERR_INVALID_ARGUMENT;
+    }
+    return launch_weight_dequant(w, s, N, K, block_size, y, static_cast<cudaStream_t>(stream));
+}
+
+int dsv3_weight_quant(const void* w, int64_t N, int64_t K, void* q, float* s, dsv3_stream_t stream) {
+    if (N < 0 || K < 0) {
+        set_last_error("weight_quant: negative size");
+        return DSV3_ERR_INVALID_ARGUMENT;
+    }
+    if (N == 0 || K == 0) return DSV3_OK;
+    if (is_null(w) || is_null(q) || is_null(s)) {
+        set_last_error("weight_quant: null pointer");
+        return DSV3_ERR_INVALID_ARGUMENT;
+    }
+    return launch_weight_quant(w, N, K, q, s, static_cast<cudaStream_t>(stream));
+}
+
+int dsv3_set_gemm_policy(int kernel, int split_k) {
+    if (kernel < 0 || kernel > 3 || split_k < 0 || split_k > 64) {
+        set_last_error("set_gemm_policy: kernel must be 0..3 and split_k 0..64");
+        return DSV3_ERR_INVALID_ARGUMENT;
+    }
+    g_force_kernel = kernel;
+    g_force_split = split_k;
+    return DSV3_OK;
+}
+
+size_t dsv3_fp8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+    if (M <= 0 || N <= 0 || K <= 0 || g_force_kernel == 1 || (K % 16) != 0) return 0;
+    const TcPlan pl = tc_plan(M, N, K, g_force_kernel, g_force_split);
+    return tc_workspace_bytes(pl, M, N);
+}
+
+int dsv3_fp8_gemm(const void* a, const float* a_s, const void* b, const float* b_s, int64_t M, int64_t N, int64_t K,
+                  void* c, void* workspace, size_t workspace_bytes, dsv3_stream_t stream) {
+    if (M < 0 || N < 0 || K < 0) {
+        set_last_error("fp8_gemm: negative size");
+        return DSV3_ERR_INVALID_ARGUMENT;
+    }
+    if (M == 0 || N == 0) return DSV3_OK;
+    if (is_null(c) || (K > 0 && (is_null(a) || is_null(a_s) || is_null(b) || is_null(b_s)))) {
+        set_last_error("fp8_gemm: null pointer");
+        return DSV3_ERR_INVALID_ARGUMENT;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (K == 0) {
+        DSV3_CUDA_TRY(cudaMemsetAsync(c, 0, static_cast<size_t>(M) * N * 2, st));
+        return DSV3_OK;
+    }
+    const bool tc_ok = tc_supported(a, b, c, M, N, K);
+    if (g_force_kernel == 1 || (!tc_ok && g_force_kernel == 0))
+        return launch_fp8_gemm_simple(a, a_s, b, b_s, M, N, K, c, st);
+    if (!tc_ok) {
+        set_last_error("fp8_gemm: the tcgen05 kernels need K %% 16 == 0 and 16-byte aligned a, b, c");
+        return DSV3_ERR_UNSUPPORTED;
+    }
+    const TcPlan pl = tc_plan(M, N, K, g_force_kernel, g_force_split);
+    return launch_fp8_gemm_tc(a, a_s, b, b_s, M, N, K, c, workspace, workspace_bytes, pl, st);
+}
+
+int dsv3_check_device_status(dsv3_stream_t stream, uint32_t detail[4]) {
+    DSV3_CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    unsigned int* dptr = status_device_ptr();
+    if (!dptr) return DSV3_ERR_CUDA;
+    unsigned int host[4] = {0, 0, 0, 0};
+    DSV3_CUDA_TRY(cudaMemcpy(host, dptr, sizeof(host), cudaMemcpyDeviceToHost));
+    if (detail) memcpy(detail, host, sizeof(host));
+    if (host[0] == 0) return DSV3_OK;
+    const unsigned int zero[4] = {0, 0, 0, 0};
+    DSV3_CUDA_TRY(cudaMemcpy(dptr, zero, sizeof(zero), cudaMemcpyHostToDevice));
+    set_last_error("device wait gave up: kind=%u (1 smem-empty, 2 smem-full, 3 tmem-empty, 4 tmem-full) chunk=%u cta=%u",
+                   host[1], host[2], host[3]);
+    return DSV3_ERR_DEVICE_TIMEOUT;
+}
+
+}  // extern "C"

@@ -1,0 +1,565 @@
+// fp8_gemm for sm_100a: TMA-fed, warp-specialised, persistent tcgen05 kernel with
+// software promotion of every 128-wide K chunk.
+//
+// Replaces inference/kernel.py:118-172 (fp8_gemm_kernel) and its launch at :194-195.
+//
+// Why promotion is done in software: the scales are fp32 (a_s per token per chunk,
+// b_s per 128x128 weight block), not ue8m0, so the block-scaled MMA kinds cannot apply
+// them.  Each chunk is therefore multiplied into its own TMEM accumulator stage
+// (4 x tcgen05.mma kind::f8f6f4, K = 32 each), read back with tcgen05.ld by the
+// promotion warps, and folded into fp32 registers as acc += dot * (a_s * b_s).
+// A ring of TMEM stages lets the tensor core run chunk i+1..i+3 while chunk i is promoted.
+//
+// Pipeline, in units of K chunks numbered g = 0,1,2,... across all work items of a CTA:
+//   warp 0 (1 lane)  TMA producer : waits empty[g % NS], loads the P and Q tiles of chunk g
+//   warp 1 (1 lane)  MMA issuer   : waits full[g % NS] and tempty[g % NT], issues 4 MMAs,
+//                                   commits to empty[g % NS] and tfull[g % NT]
+//   warps 4..11      promotion    : wait tfull[g % NT], tcgen05.ld, release tempty, FMA;
+//                                   at the end of a work item write C (or a split-K partial)
+// Operand roles: P is the 128-row MMA "A" operand, Q the BN-row MMA "B" operand.
+//   kSwap = false : P = 128 tokens of a,  Q = 128 rows of b  (large M)
+//   kSwap = true  : P = 128 rows of b,    Q = BN tokens of a (small M, weights stream once)
+// Split-K: a work item is (tile, split); partial sums go to a workspace and the CTA that
+// takes the last ticket of a tile adds them in split order (deterministic, no spinning).
+//
+// Every wait is bounded: after about a second the waiting thread records what it was
+// waiting for in the status word, raises a CTA-wide abort flag and all roles fall
+// through to the common teardown (which frees TMEM).
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace dsv3 {
+
+namespace {
+
+constexpr int kNumThreads = 384;          // warps 0..3: producer, MMA, 2 spare; warps 4..11: promotion
+constexpr int kPromoThreads = 256;
+constexpr int kPRows = 128;               // MMA M
+constexpr int kChunk = 128;               // K elements (= bytes) per chunk
+constexpr int kTmemStages = 4;
+constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;
+constexpr int kMaxTickets = DSV3_WORKSPACE_HEADER_BYTES / 4;
+
+struct TcParams {
+    const float* a_s;
+    const float* b_s;
+    __nv_bfloat16* c;
+    float* partials;        // [splits][M][N] fp32, only when splits > 1
+    int* tickets;           // one per tile, zero on entry and on exit
+    unsigned int* status;   // device status words
+    int64_t M, N;
+    int kc;                 // number of K chunks
+    int tiles_p, tiles_q;
+    int splits;
+    int num_items;          // tiles_p * tiles_q * splits
+};
+
+template <int BN>
+struct Cfg {
+    static constexpr int kStageBytes = kPRows * kChunk + BN * kChunk;
+    static constexpr int kStagesRaw = (192 * 1024) / kStageBytes;
+    static constexpr int kStages = kStagesRaw > 10 ? 10 : kStagesRaw;
+    static constexpr int kTmemCols = kTmemStages * BN;  // 64..512, a power of two
+    // tiles + barriers + control words + slack for the 1024-byte alignment of the tiles
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 1024;
+    static_assert(kTmemCols >= 32 && kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "TMEM columns");
+    static_assert((BN * kChunk) % 1024 == 0, "Q tile must keep 1024-byte alignment");
+    // more than half of an SM's shared memory, so two CTAs can never share an SM (and its TMEM)
+    static_assert(kSmemBytes > 116 * 1024, "one CTA per SM");
+};
+
+struct Control {
+    volatile uint32_t abort_flag;
+    uint32_t tmem_base;
+    volatile int ticket;
+};
+
+__device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, Control* ctl, unsigned int* status,
+                                             uint32_t what, uint32_t g) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    uint32_t spins = 0;
+    for (;;) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((++spins & 31u) == 0) {
+            if (ctl->abort_flag) return false;
+            if (global_timer_ns() - t0 > kWaitLimitNs) {
+                ctl->abort_flag = 1;
+                if (atomicCAS(&status[0], 0u, 1u) == 0u) {
+                    status[1] = what;        // 1 empty, 2 full, 3 tmem-empty, 4 tmem-full
+                    status[2] = g;           // chunk counter of the waiting role
+                    status[3] = blockIdx.x;
+                }
+                return false;
+            }
+        }
+    }
+}
+
+struct Item {
+    int p_idx, q_idx, split, tile;
+    int c0, c1;  // chunk range
+};
+
+__device__ __forceinline__ Item decode_item(int item, const TcParams& p) {
+    Item it;
+    it.tile = item / p.splits;
+    it.split = item - it.tile * p.splits;
+    // grouped raster: 8 P-tiles share consecutive Q-tiles so a wave re-uses both operands in L2
+    constexpr int kGroup = 8;
+    const int per_group = kGroup * p.tiles_q;
+    const int grp = it.tile / per_group;
+    const int first_p = grp * kGroup;
+    const int gsz = min(kGroup, p.tiles_p - first_p);
+    const int r = it.tile - grp * per_group;
+    it.p_idx = first_p + r % gsz;
+    it.q_idx = r / gsz;
+    it.c0 = static_cast<int>((static_cast<int64_t>(p.kc) * it.split) / p.splits);
+    it.c1 = static_cast<int>((static_cast<int64_t>(p.kc) * (it.split + 1)) / p.splits);
+    return it;
+}
+
+template <int N>
+__device__ __forceinline__ void tmem_load_cols(uint32_t taddr, uint32_t* v) {
+    if constexpr (N == 8) {
+        tc_ld_x8(taddr, v);
+    } else if constexpr (N == 16) {
+        tc_ld_x16(taddr, v);
+    } else if constexpr (N == 32) {
+        tc_ld_x32(taddr, v);
+    } else {
+        static_assert(N == 64, "columns per thread");
+        tc_ld_x32(taddr, v);
+        tc_ld_x32(taddr + 32, v + 32);
+    }
+}
+
+__device__ __forceinline__ void promo_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(kPromoThreads) : "memory"); }
+
+template <int BN, bool kSwap>
+__global__ void __launch_bounds__(kNumThreads, 1)
+fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constant__ CUtensorMap tmap_q,
+                   const TcParams p) {
+    using C = Cfg<BN>;
+    constexpr int NS = C::kStages;
+    constexpr int NT = kTmemStages;
+    constexpr int CPT = BN / 2;  // accumulator columns per promotion thread
+    static_assert(kSwap || BN == 128, "token-major tiles are 128 x 128 (one b_s value per tile and chunk)");
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t tiles = (raw + 1023u) & ~1023u;
+    uint8_t* gen_tiles = smem_raw + (tiles - raw);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(gen_tiles + NS * C::kStageBytes);
+    Control* ctl = reinterpret_cast<Control*>(bars + 2 * NS + 2 * NT);
+    const uint32_t bar0 = smem_u32(bars);
+    auto full_bar = [&](int s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (NS + s); };
+    auto tfull_bar = [&](int s) { return bar0 + 8u * (2 * NS + s); };
+    auto tempty_bar = [&](int s) { return bar0 + 8u * (2 * NS + NT + s); };
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NS; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int s = 0; s < NT; ++s) {
+            mbar_init(tfull_bar(s), 1);
+            mbar_init(tempty_bar(s), kPromoThreads / 32);
+        }
+        ctl->abort_flag = 0;
+        ctl->ticket = 0;
+        mbar_fence_init();
+        tma_prefetch_desc(&tmap_p);
+        tma_prefetch_desc(&tmap_q);
+    }
+    if (warp == 1) tc_alloc(smem_u32(&ctl->tmem_base), C::kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = ctl->tmem_base;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            uint32_t g = 0;
+            bool ok = true;
+            for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
+                const Item it = decode_item(item, p);
+                const int p_row = it.p_idx * kPRows, q_row = it.q_idx * BN;
+                for (int ch = it.c0; ch < it.c1; ++ch, ++g) {
+                    const int s = g % NS;
+                    ok = bounded_wait(empty_bar(s), ((g / NS) & 1u) ^ 1u, ctl, p.status, 1, g);
+                    if (!ok) break;
+                    const uint32_t dst = tiles + s * C::kStageBytes;
+                    mbar_arrive_expect_tx(full_bar(s), C::kStageBytes);
+                    tma_load_2d(dst, &tmap_p, ch * kChunk, p_row, full_bar(s));
+                    tma_load_2d(dst + kPRows * kChunk, &tmap_q, ch * kChunk, q_row, full_bar(s));
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_e4m3_f32(kPRows, BN);
+            uint32_t g = 0;
+            bool ok = true;
+            for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
+                const Item it = decode_item(item, p);
+                for (int ch = it.c0; ch < it.c1; ++ch, ++g) {
+                    const int s = g % NS, ts = g % NT;
+                    ok = bounded_wait(tempty_bar(ts), ((g / NT) & 1u) ^ 1u, ctl, p.status, 3, g) &&
+                         bounded_wait(full_bar(s), (g / NS) & 1u, ctl, p.status, 2, g);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t sp = tiles + s * C::kStageBytes;
+                    const uint64_t dp = umma_desc_k_major_sw128(sp);
+                    const uint64_t dq = umma_desc_k_major_sw128(sp + kPRows * kChunk);
+                    const uint32_t d_tmem = tmem_base + ts * BN;
+#pragma unroll
+                    for (int k = 0; k < kChunk / 32; ++k) {
+                        // 32 bytes further along K inside the 128-byte swizzle atom: +2 in address units of 16 B
+                        tc_mma_f8(d_tmem, dp + 2u * k, dq + 2u * k, idesc, k > 0 ? 1u : 0u);
+                    }
+                    tc_commit(empty_bar(s));   // smem stage reusable once these MMAs have read it
+                    tc_commit(tfull_bar(ts));  // chunk product complete in TMEM
+                }
+            }
+        }
+    } else if (warp >= 4) {
+        // ------------------------------------------------------------ promotion + epilogue
+        const int pw = warp - 4;
+        const int quarter = warp & 3;           // TMEM lane quarter this warp may access
+        const int half = pw >> 2;               // which half of the BN columns
+        const int row = quarter * 32 + lane;    // accumulator row (TMEM lane)
+        const int col0 = half * CPT;
+        const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + col0;
+        const int64_t M = p.M, N = p.N;
+        const int kc = p.kc;
+        uint32_t g = 0;
+        bool ok = true;
+        for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
+            const Item it = decode_item(item, p);
+            float acc[CPT];
+#pragma unroll
+            for (int j = 0; j < CPT; ++j) acc[j] = 0.0f;
+
+            // token / weight-row coordinates of this thread
+            const int64_t p_row = static_cast<int64_t>(it.p_idx) * kPRows + row;
+            const int64_t q_base = static_cast<int64_t>(it.q_idx) * BN + col0;
+            const float* as_ptr;  // normal: this row's scales ; swap: scales of token q_base
+            const float* bs_ptr;
+            if constexpr (!kSwap) {
+                as_ptr = p.a_s + min(p_row, M - 1) * kc;
+                bs_ptr = p.b_s + static_cast<int64_t>(it.q_idx) * kc;          // BN == 128
+            } else {
+                as_ptr = p.a_s;
+                bs_ptr = p.b_s + static_cast<int64_t>(it.p_idx) * kc;          // 128 weight rows = one scale row
+            }
+
+            for (int ch = it.c0; ch < it.c1; ++ch, ++g) {
+                const int ts = g % NT;
+                float sc[kSwap ? CPT : 1];
+                const float bs = __ldg(bs_ptr + ch);
+                if constexpr (!kSwap) {
+                    sc[0] = __ldg(as_ptr + ch) * bs;
+                } else {
+#pragma unroll
+                    for (int j = 0; j < CPT; ++j) {
+                        const int64_t m = min(q_base + j, M - 1);
+                        sc[j] = __ldg(as_ptr + m * kc + ch) * bs;
+                    }
+                }
+                bool mine = bounded_wait(tfull_bar(ts), (g / NT) & 1u, ctl, p.status, 4, g);
+                ok = __all_sync(0xffffffffu, mine);
+                if (!ok) break;
+                tc_fence_after();
+                uint32_t v[CPT];
+                tmem_load_cols<CPT>(t_lane + ts * BN, v);
+                tc_wait_ld();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tempty_bar(ts));
+#pragma unroll
+                for (int j = 0; j < CPT; ++j) acc[j] = fmaf(__uint_as_float(v[j]), sc[kSwap ? j : 0], acc[j]);
+            }
+            if (!ok) break;
+
+            // ---------------------------------------------------- write-out
+            // normal: thread = token row, CPT consecutive output columns
+            // swap  : thread = output column (weight row), CPT tokens
+            if (p.splits == 1) {
+                if constexpr (!kSwap) {
+                    if (p_row < M) {
+                        __nv_bfloat16* crow = p.c + p_row * N;
+                        const bool vec_ok = (N % 8) == 0;
+#pragma unroll
+                        for (int j = 0; j < CPT; j += 8) {
+                            const int64_t n = q_base + j;
+                            if (vec_ok && n + 8 <= N) {
+                                uint4 o = make_uint4(pack_bf16x2(acc[j], acc[j + 1]), pack_bf16x2(acc[j + 2], acc[j + 3]),
+                                                     pack_bf16x2(acc[j + 4], acc[j + 5]), pack_bf16x2(acc[j + 6], acc[j + 7]));
+                                *reinterpret_cast<uint4*>(crow + n) = o;
+                            } else {
+#pragma unroll
+                                for (int e = 0; e < 8; ++e)
+                                    if (n + e < N) crow[n + e] = __float2bfloat16_rn(acc[j + e]);
+                            }
+                        }
+                    }
+                } else {
+                    if (p_row < N) {
+#pragma unroll
+                        for (int j = 0; j < CPT; ++j) {
+                            const int64_t m = q_base + j;
+                            if (m < M) p.c[m * N + p_row] = __float2bfloat16_rn(acc[j]);
+                        }
+                    }
+                }
+            } else {
+                float* part = p.partials + static_cast<int64_t>(it.split) * M * N;
+                if constexpr (!kSwap) {
+                    if (p_row < M) {
+#pragma unroll
+                        for (int j = 0; j < CPT; ++j) {
+                            const int64_t n = q_base + j;
+                            if (n < N) __stcg(part + p_row * N + n, acc[j]);
+                        }
+                    }
+                } else {
+                    if (p_row < N) {
+#pragma unroll
+                        for (int j = 0; j < CPT; ++j) {
+                            const int64_t m = q_base + j;
+                            if (m < M) __stcg(part + m * N + p_row, acc[j]);
+                        }
+                    }
+                }
+                __threadfence();
+                promo_barrier();
+                if (threadIdx.x == 4 * 32) {
+                    const int t = atomicAdd(p.tickets + it.tile, 1);
+                    if (t == p.splits - 1) p.tickets[it.tile] = 0;  // last arrival: leave the ticket clean
+                    ctl->ticket = t;
+                }
+                promo_barrier();
+                const bool last = (ctl->ticket == p.splits - 1);
+                promo_barrier();  // everyone has read the ticket before the next item overwrites it
+                if (last) {
+                    __threadfence();
+                    if constexpr (!kSwap) {
+                        if (p_row < M) {
+#pragma unroll
+                            for (int j = 0; j < CPT; ++j) {
+                                const int64_t n = q_base + j;
+                                if (n < N) {
+                                    float sum = 0.0f;
+                                    for (int s = 0; s < p.splits; ++s)
+                                        sum += __ldcg(p.partials + (static_cast<int64_t>(s) * M + p_row) * N + n);
+                                    p.c[p_row * N + n] = __float2bfloat16_rn(sum);
+                                }
+                            }
+                        }
+                    } else {
+                        if (p_row < N) {
+#pragma unroll
+                            for (int j = 0; j < CPT; ++j) {
+                                const int64_t m = q_base + j;
+                                if (m < M) {
+                                    float sum = 0.0f;
+                                    for (int s = 0; s < p.splits; ++s)
+                                        sum += __ldcg(p.partials + (static_cast<int64_t>(s) * M + m) * N + p_row);
+                                    p.c[m * N + p_row] = __float2bfloat16_rn(sum);
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
+    if (ctl->abort_flag) {
+        // give copies and MMAs that were already issued time to land before the CTA's
+        // shared memory and TMEM are released
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        tc_dealloc(tmem_base, C::kTmemCols);
+    }
+}
+
+// -------------------------------------------------------------------- host side
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    });
+    return fn;
+}
+
+// [rows, K] bytes, row-major; box = 128 bytes x box_rows, 128-byte swizzle, zero fill outside.
+int make_tmap(CUtensorMap* map, const void* base, int64_t rows, int64_t K, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) {
+        set_last_error("cuTensorMapEncodeTiled is not available from the driver");
+        return DSV3_ERR_CUDA;
+    }
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K)};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(kChunk), static_cast<cuuint32_t>(box_rows)};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_last_error("cuTensorMapEncodeTiled failed with CUresult %d (rows=%lld K=%lld box_rows=%d)", static_cast<int>(r),
+                       static_cast<long long>(rows), static_cast<long long>(K), box_rows);
+        return DSV3_ERR_CUDA;
+    }
+    return DSV3_OK;
+}
+
+template <int BN, bool kSwap>
+int launch_variant(const CUtensorMap& tp, const CUtensorMap& tq, const TcParams& prm, cudaStream_t stream) {
+    using C = Cfg<BN>;
+    auto kern = fp8_gemm_tc_kernel<BN, kSwap>;
+    static bool configured[64] = {};
+    int dev = 0;
+    DSV3_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 64 && !configured[dev]) {
+        DSV3_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+        configured[dev] = true;
+    }
+    int grid = prm.num_items < num_sms() ? prm.num_items : num_sms();
+    kern<<<grid, kNumThreads, C::kSmemBytes, stream>>>(tp, tq, prm);
+    DSV3_CUDA_TRY(cudaGetLastError());
+    return DSV3_OK;
+}
+
+}  // namespace
+
+// Geometry chosen for a problem; shared by the workspace query and the launch.
+struct TcPlan {
+    bool swap;
+    int bn;
+    int tiles_p, tiles_q, splits, kc;
+};
+
+bool tc_supported(const void* a, const void* b, const void* c, int64_t M, int64_t N, int64_t K) {
+    return M > 0 && N > 0 && K >= 16 && (K % 16) == 0 && (reinterpret_cast<uintptr_t>(a) % 16) == 0 &&
+           (reinterpret_cast<uintptr_t>(b) % 16) == 0 && (reinterpret_cast<uintptr_t>(c) % 16) == 0 && M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31);
+}
+
+TcPlan tc_plan(int64_t M, int64_t N, int64_t K, int force_kernel, int force_split) {
+    TcPlan pl;
+    pl.kc = static_cast<int>((K + kChunk - 1) / kChunk);
+    pl.swap = (force_kernel == 3) || (force_kernel != 2 && M <= 64);
+    if (pl.swap) {
+        pl.bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+        pl.tiles_p = static_cast<int>((N + kPRows - 1) / kPRows);
+        pl.tiles_q = static_cast<int>((M + pl.bn - 1) / pl.bn);
+    } else {
+        pl.bn = 128;
+        pl.tiles_p = static_cast<int>((M + kPRows - 1) / kPRows);
+        pl.tiles_q = static_cast<int>((N + 127) / 128);
+    }
+    const int64_t tiles = static_cast<int64_t>(pl.tiles_p) * pl.tiles_q;
+    int splits = 1;
+    if (force_split > 0) {
+        splits = force_split;
+    } else {
+        const int sms = num_sms();
+        if (tiles * 2 <= sms) {
+            splits = static_cast<int>((sms + tiles - 1) / tiles);  // enough items for one wave
+            const int max_by_k = pl.kc / 2 > 0 ? pl.kc / 2 : 1;     // at least two chunks per split
+            if (splits > max_by_k) splits = max_by_k;
+            if (splits > 32) splits = 32;
+        }
+    }
+    if (splits > pl.kc) splits = pl.kc;
+    if (splits < 1) splits = 1;
+    if (tiles > kMaxTickets) splits = 1;
+    pl.splits = splits;
+    return pl;
+}
+
+size_t tc_workspace_bytes(const TcPlan& pl, int64_t M, int64_t N) {
+    if (pl.splits <= 1) return 0;
+    return static_cast<size_t>(DSV3_WORKSPACE_HEADER_BYTES) + static_cast<size_t>(pl.splits) * M * N * sizeof(float);
+}
+
+int launch_fp8_gemm_tc(const void* a, const float* a_s, const void* b, const float* b_s, int64_t M, int64_t N,
+                       int64_t K, void* c, void* workspace, size_t workspace_bytes, const TcPlan& pl,
+                       cudaStream_t stream) {
+    if (pl.splits > 1) {
+        const size_t need = tc_workspace_bytes(pl, M, N);
+        if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) % 256) != 0) {
+            set_last_error("fp8_gemm: split-K needs a 256-byte aligned workspace of %zu bytes (got %zu)", need,
+                           workspace ? workspace_bytes : static_cast<size_t>(0));
+            return DSV3_ERR_WORKSPACE;
+        }
+    }
+    CUtensorMap tp, tq;
+    int rc;
+    if (pl.swap) {
+        if ((rc = make_tmap(&tp, b, N, K, kPRows)) != DSV3_OK) return rc;
+        if ((rc = make_tmap(&tq, a, M, K, pl.bn)) != DSV3_OK) return rc;
+    } else {
+        if ((rc = make_tmap(&tp, a, M, K, kPRows)) != DSV3_OK) return rc;
+        if ((rc = make_tmap(&tq, b, N, K, pl.bn)) != DSV3_OK) return rc;
+    }
+    TcParams prm;
+    prm.a_s = a_s;
+    prm.b_s = b_s;
+    prm.c = static_cast<__nv_bfloat16*>(c);
+    prm.tickets = static_cast<int*>(workspace);
+    prm.partials = workspace ? reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + DSV3_WORKSPACE_HEADER_BYTES)
+                             : nullptr;
+    prm.status = status_device_ptr();
+    if (!prm.status) return DSV3_ERR_CUDA;
+    prm.M = M;
+    prm.N = N;
+    prm.kc = pl.kc;
+    prm.tiles_p = pl.tiles_p;
+    prm.tiles_q = pl.tiles_q;
+    prm.splits = pl.splits;
+    prm.num_items = pl.tiles_p * pl.tiles_q * pl.splits;
+    if (pl.swap) {
+        switch (pl.bn) {
+            case 16: return launch_variant<16, true>(tp, tq, prm, stream);
+            case 32: return launch_variant<32, true>(tp, tq, prm, stream);
+            case 64: return launch_variant<64, true>(tp, tq, prm, stream);
+        }
+    } else if (pl.bn == 128) {
+        return launch_variant<128, false>(tp, tq, prm, stream);
+    }
+    set_last_error("fp8_gemm: no tcgen05 variant for tile width %d", pl.bn);
+    return DSV3_ERR_UNSUPPORTED;
+}
+
+}  // namespace dsv3

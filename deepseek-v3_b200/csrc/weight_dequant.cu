@@ -1,0 +1,127 @@
+// weight_dequant / weight_quant for sm_100a.
+//
+// weight_dequant replaces inference/kernel.py:60-86 (weight_dequant_kernel) and its
+// launch at :108-109: y[n,k] = bf16_rn(float(w[n,k]) * s[n/block, k/block]).  The
+// reference moves one byte per load; here a thread converts 16 FP8 bytes (one 16-byte
+// load) into 16 bf16 values (two 16-byte stores) and the grid is sized from the SM count.
+//
+// weight_quant is the harness-side inverse (the reference ships none): per 128x128
+// block s = max(amax,1e-4)/448 with IEEE division, q = e4m3_rn(w / s).
+#include "common.cuh"
+
+namespace dsv3 {
+
+namespace {
+
+constexpr int kThreads = 256;
+
+__device__ __forceinline__ uint4 dequant8(uint32_t lo, uint32_t hi, float s) {
+    const float2 a = e4m3x2_to_float2(static_cast<uint16_t>(lo & 0xFFFFu));
+    const float2 b = e4m3x2_to_float2(static_cast<uint16_t>(lo >> 16));
+    const float2 c = e4m3x2_to_float2(static_cast<uint16_t>(hi & 0xFFFFu));
+    const float2 d = e4m3x2_to_float2(static_cast<uint16_t>(hi >> 16));
+    return make_uint4(pack_bf16x2(__fmul_rn(a.x, s), __fmul_rn(a.y, s)), pack_bf16x2(__fmul_rn(b.x, s), __fmul_rn(b.y, s)),
+                      pack_bf16x2(__fmul_rn(c.x, s), __fmul_rn(c.y, s)), pack_bf16x2(__fmul_rn(d.x, s), __fmul_rn(d.y, s)));
+}
+
+// K % 16 == 0: a 16-element group never straddles a scale block (block % 16 == 0).
+__global__ void __launch_bounds__(kThreads) weight_dequant_vec_kernel(const uint4* __restrict__ w,
+                                                                       const float* __restrict__ s,
+                                                                       uint4* __restrict__ y, int64_t N, int64_t K,
+                                                                       int block, int64_t kb) {
+    const int64_t groups_per_row = K >> 4;
+    const int64_t total = N * groups_per_row;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
+    for (int64_t g = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; g < total; g += stride) {
+        const int64_t n = g / groups_per_row;
+        const int64_t k = (g - n * groups_per_row) << 4;
+        const float sc = __ldg(s + (n / block) * kb + (k / block));
+        const uint4 v = __ldcs(w + g);
+        __stcs(y + 2 * g, dequant8(v.x, v.y, sc));
+        __stcs(y + 2 * g + 1, dequant8(v.z, v.w, sc));
+    }
+}
+
+// Any K / alignment / block size: one element per thread.
+__global__ void __launch_bounds__(kThreads) weight_dequant_scalar_kernel(const uint8_t* __restrict__ w,
+                                                                          const float* __restrict__ s,
+                                                                          __nv_bfloat16* __restrict__ y, int64_t N,
+                                                                          int64_t K, int block, int64_t kb) {
+    const int64_t total = N * K;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < total; i += stride) {
+        const int64_t n = i / K, k = i - n * K;
+        const float2 f = e4m3x2_to_float2(static_cast<uint16_t>(w[i]));
+        y[i] = __float2bfloat16_rn(__fmul_rn(f.x, s[(n / block) * kb + (k / block)]));
+    }
+}
+
+// One CTA per 128x128 block; thread t owns 16-byte column segment (t % 8) of rows t/8, t/8+32, ...
+__global__ void __launch_bounds__(kThreads) weight_quant_kernel(const __nv_bfloat16* __restrict__ w,
+                                                                 uint8_t* __restrict__ q, float* __restrict__ s,
+                                                                 int64_t N, int64_t K, int64_t kb) {
+    __shared__ float red[kThreads / 32];
+    const int64_t n0 = static_cast<int64_t>(blockIdx.y) * 128, k0 = static_cast<int64_t>(blockIdx.x) * 128;
+    float m = 0.0f;
+    for (int e = threadIdx.x; e < 128 * 128; e += kThreads) {
+        const int64_t n = n0 + (e >> 7), k = k0 + (e & 127);
+        if (n < N && k < K) m = fmaxf(m, fabsf(__bfloat162float(w[n * K + k])));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+    __syncthreads();
+    m = red[0];
+#pragma unroll
+    for (int i = 1; i < kThreads / 32; ++i) m = fmaxf(m, red[i]);
+    const float sc = __fdiv_rn(fmaxf(m, 1e-4f), 448.0f);
+    for (int e = threadIdx.x; e < 128 * 128; e += kThreads) {
+        const int64_t n = n0 + (e >> 7), k = k0 + (e & 127);
+        if (n < N && k < K) {
+            const float v = __fdiv_rn(__bfloat162float(w[n * K + k]), sc);
+            q[n * K + k] = static_cast<uint8_t>(cvt_e4m3x2(v, 0.0f) & 0xFFu);
+        }
+    }
+    if (threadIdx.x == 0) s[static_cast<int64_t>(blockIdx.y) * kb + blockIdx.x] = sc;
+}
+
+}  // namespace
+
+int launch_weight_dequant(const void* w, const float* s, int64_t N, int64_t K, int block, void* y,
+                          cudaStream_t stream) {
+    if (N == 0 || K == 0) return DSV3_OK;
+    const int64_t kb = (K + block - 1) / block;
+    const int64_t cap = static_cast<int64_t>(num_sms()) * 8;
+    const bool vec = (K % 16 == 0) && (block % 16 == 0) && (reinterpret_cast<uintptr_t>(w) % 16 == 0) &&
+                     (reinterpret_cast<uintptr_t>(y) % 16 == 0);
+    if (vec) {
+        const int64_t total = N * (K >> 4);
+        int64_t grid = (total + kThreads - 1) / kThreads;
+        if (grid > cap) grid = cap;
+        weight_dequant_vec_kernel<<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
+            static_cast<const uint4*>(w), s, static_cast<uint4*>(y), N, K, block, kb);
+    } else {
+        int64_t grid = (N * K + kThreads - 1) / kThreads;
+        if (grid > cap) grid = cap;
+        weight_dequant_scalar_kernel<<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
+            static_cast<const uint8_t*>(w), s, static_cast<__nv_bfloat16*>(y), N, K, block, kb);
+    }
+    DSV3_CUDA_TRY(cudaGetLastError());
+    return DSV3_OK;
+}
+
+int launch_weight_quant(const void* w, int64_t N, int64_t K, void* q, float* s, cudaStream_t stream) {
+    if (N == 0 || K == 0) return DSV3_OK;
+    const int64_t nb = (N + 127) / 128, kb = (K + 127) / 128;
+    if (nb > 65535) {
+        set_last_error("weight_quant: N=%lld exceeds the grid limit", static_cast<long long>(N));
+        return DSV3_ERR_UNSUPPORTED;
+    }
+    dim3 grid(static_cast<unsigned>(kb), static_cast<unsigned>(nb));
+    weight_quant_kernel<<<grid, kThreads, 0, stream>>>(static_cast<const __nv_bfloat16*>(w),
+                                                       static_cast<uint8_t*>(q), s, N, K, kb);
+    DSV3_CUDA_TRY(cudaGetLastError());
+    return DSV3_OK;
+}
+
+}  // namespace dsv3

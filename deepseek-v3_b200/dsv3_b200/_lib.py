@@ -1,0 +1,67 @@
+"""ctypes binding of libdsv3_b200.so (the C ABI declared in include/dsv3_b200.h).
+
+The library is built in-tree by ``deepseek-v3_b200/build.py``.  There is no other
+implementation behind these functions: if the shared object is missing the import
+fails, and tensors that are not on a CUDA device are rejected.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(os.path.dirname(_HERE), "lib", "libdsv3_b200.so")
+
+OK = 0
+ERR_INVALID_ARGUMENT = -1
+ERR_UNSUPPORTED = -2
+ERR_CUDA = -3
+ERR_WORKSPACE = -4
+ERR_DEVICE_TIMEOUT = -5
+WORKSPACE_HEADER_BYTES = 16384
+
+EXPORTS = (
+    "dsv3_version", "dsv3_strerror", "dsv3_last_error", "dsv3_act_quant", "dsv3_weight_dequant",
+    "dsv3_fp8_gemm_workspace_bytes", "dsv3_fp8_gemm", "dsv3_set_gemm_policy", "dsv3_weight_quant",
+    "dsv3_check_device_status",
+)
+
+
+class Dsv3Error(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(message)
+        self.status = status
+
+
+def _load() -> ctypes.CDLL:
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python deepseek-v3_b200/build.py` "
+            "(there is no fallback implementation)")
+    lib = ctypes.CDLL(LIB_PATH)
+    i64, vp, ci, sz = ctypes.c_int64, ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
+    lib.dsv3_version.restype = ci
+    lib.dsv3_strerror.argtypes = [ci]
+    lib.dsv3_strerror.restype = ctypes.c_char_p
+    lib.dsv3_last_error.restype = ctypes.c_char_p
+    lib.dsv3_act_quant.argtypes = [vp, i64, i64, ci, ci, vp, vp, vp]
+    lib.dsv3_weight_dequant.argtypes = [vp, vp, i64, i64, ci, vp, vp]
+    lib.dsv3_fp8_gemm_workspace_bytes.argtypes = [i64, i64, i64]
+    lib.dsv3_fp8_gemm_workspace_bytes.restype = sz
+    lib.dsv3_fp8_gemm.argtypes = [vp, vp, vp, vp, i64, i64, i64, vp, vp, sz, vp]
+    lib.dsv3_set_gemm_policy.argtypes = [ci, ci]
+    lib.dsv3_weight_quant.argtypes = [vp, i64, i64, vp, vp, vp]
+    lib.dsv3_check_device_status.argtypes = [vp, ctypes.POINTER(ctypes.c_uint32 * 4)]
+    for name in ("dsv3_act_quant", "dsv3_weight_dequant", "dsv3_fp8_gemm", "dsv3_set_gemm_policy",
+                 "dsv3_weight_quant", "dsv3_check_device_status"):
+        getattr(lib, name).restype = ci
+    return lib
+
+
+lib = _load()
+
+
+def check(status: int) -> None:
+    if status != OK:
+        detail = lib.dsv3_last_error().decode(errors="replace")
+        raise Dsv3Error(status, f"{lib.dsv3_strerror(status).decode()} ({status}): {detail}")

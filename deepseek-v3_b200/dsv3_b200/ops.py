@@ -1,0 +1,146 @@
+"""The three operators of the reference's ``inference/kernel.py`` on sm_100a.
+
+Signatures, argument meaning, allocation behaviour and assertion messages follow
+``kernel.py`` (``act_quant`` :38-57, ``weight_dequant`` :89-110, ``fp8_gemm``
+:175-196) so that ``model.py`` and ``generate.py`` run unchanged on top of them.
+The work is done by hand-written CUDA behind a C ABI; tensors must live on a CUDA
+device and nothing here falls back to another implementation.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import lib
+
+KERNEL_AUTO, KERNEL_CUDA_CORE, KERNEL_TC_TOKEN_MAJOR, KERNEL_TC_WEIGHT_MAJOR = 0, 1, 2, 3
+
+_workspaces: Dict[Tuple[int, int], torch.Tensor] = {}
+
+
+def _require_cuda(*tensors: torch.Tensor) -> torch.device:
+    dev = tensors[0].device
+    for t in tensors:
+        if t.device.type != "cuda":
+            raise RuntimeError("dsv3_b200 runs on CUDA tensors only (there is no CPU path); got a "
+                               f"{t.device.type} tensor")
+        if t.device != dev:
+            raise RuntimeError("all tensors of one call must be on the same device")
+    return dev
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _out_dtype() -> torch.dtype:
+    dt = torch.get_default_dtype()
+    if dt != torch.bfloat16:
+        raise NotImplementedError(
+            "the CUDA path writes bfloat16 only; call torch.set_default_dtype(torch.bfloat16) "
+            f"as every entry point of the reference does (default dtype is {dt})")
+    return dt
+
+
+def _workspace(dev: torch.device, nbytes: int) -> Optional[torch.Tensor]:
+    """Scratch for split-K, one per (device, stream); its header must be zero on first use and
+    every call leaves it zero again."""
+    if nbytes == 0:
+        return None
+    key = (dev.index if dev.index is not None else torch.cuda.current_device(), _stream())
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        size = max(nbytes, 8 << 20)
+        ws = torch.zeros(size, dtype=torch.uint8, device=dev)
+        _workspaces[key] = ws
+    return ws
+
+
+def act_quant(x: torch.Tensor, block_size: int = 128, scale_fmt: Optional[str] = None
+              ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Block-wise FP8 quantisation of activations (kernel.py:38-57).
+
+    Returns ``(y, s)``: ``y`` float8_e4m3fn of x's shape, ``s`` float32 of shape
+    ``[..., K // block_size]`` with ``s = max(amax, 1e-4) / 448`` per block (rounded up to a
+    power of two when ``scale_fmt == "ue8m0"``).
+    """
+    assert x.is_contiguous(), 'Input tensor must be contiguous'
+    assert x.size(-1) % block_size == 0, \
+        f'Last dimension size must be divisible by block_size (block_size={block_size})'
+    dev = _require_cuda(x)
+    if x.dtype != torch.bfloat16:
+        raise NotImplementedError(f"act_quant takes bfloat16 activations (got {x.dtype})")
+    y = torch.empty_like(x, dtype=torch.float8_e4m3fn)
+    s = x.new_empty(*x.size()[:-1], x.size(-1) // block_size, dtype=torch.float32)
+    K = x.size(-1)
+    rows = x.numel() // K if K else 0
+    with torch.cuda.device(dev):
+        _lib.check(lib.dsv3_act_quant(x.data_ptr(), rows, K, block_size, 1 if scale_fmt == "ue8m0" else 0,
+                                      y.data_ptr(), s.data_ptr(), _stream()))
+    return y, s
+
+
+def weight_dequant(x: torch.Tensor, s: torch.Tensor, block_size: int = 128) -> torch.Tensor:
+    """De-quantise a block-scaled FP8 weight to the default dtype (kernel.py:89-110)."""
+    assert x.is_contiguous() and s.is_contiguous(), 'Input tensors must be contiguous'
+    assert x.dim() == 2 and s.dim() == 2, 'Input tensors must have 2 dimensions'
+    dev = _require_cuda(x, s)
+    if x.element_size() != 1 or s.dtype != torch.float32:
+        raise NotImplementedError("weight_dequant takes a 1-byte FP8 weight and float32 scales")
+    M, N = x.size()
+    y = torch.empty_like(x, dtype=_out_dtype())
+    with torch.cuda.device(dev):
+        _lib.check(lib.dsv3_weight_dequant(x.data_ptr(), s.data_ptr(), M, N, block_size, y.data_ptr(), _stream()))
+    return y
+
+
+def fp8_gemm(a: torch.Tensor, a_s: torch.Tensor, b: torch.Tensor, b_s: torch.Tensor) -> torch.Tensor:
+    """Block-scaled FP8 GEMM ``c = a @ b.T`` with fp32 accumulation (kernel.py:175-196)."""
+    assert a.is_contiguous() and b.is_contiguous(), 'Input tensors must be contiguous'
+    assert a_s.is_contiguous() and b_s.is_contiguous(), 'Scaling factor tensors must be contiguous'
+    dev = _require_cuda(a, a_s, b, b_s)
+    if a.element_size() != 1 or b.element_size() != 1 or a_s.dtype != torch.float32 or b_s.dtype != torch.float32:
+        raise NotImplementedError("fp8_gemm takes 1-byte FP8 operands and float32 scales")
+    K = a.size(-1)
+    M = a.numel() // K
+    N = b.size(0)
+    c = a.new_empty(*a.size()[:-1], N, dtype=_out_dtype())
+    with torch.cuda.device(dev):
+        ws = _workspace(dev, lib.dsv3_fp8_gemm_workspace_bytes(M, N, K))
+        _lib.check(lib.dsv3_fp8_gemm(a.data_ptr(), a_s.data_ptr(), b.data_ptr(), b_s.data_ptr(), M, N, K,
+                                     c.data_ptr(), ws.data_ptr() if ws is not None else None,
+                                     ws.numel() if ws is not None else 0, _stream()))
+    return c
+
+
+def weight_quant(w: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Harness quantiser: bf16 ``[N, K]`` -> (float8_e4m3fn ``[N, K]``, float32 ``[ceil(N/128), ceil(K/128)]``)
+    with ``s = max(amax, 1e-4) / 448`` per 128x128 block; the inverse of ``weight_dequant``."""
+    assert w.is_contiguous() and w.dim() == 2
+    dev = _require_cuda(w)
+    if w.dtype != torch.bfloat16:
+        raise NotImplementedError("weight_quant takes a bfloat16 weight")
+    N, K = w.shape
+    q = torch.empty_like(w, dtype=torch.float8_e4m3fn)
+    s = w.new_empty((N + 127) // 128, (K + 127) // 128, dtype=torch.float32)
+    with torch.cuda.device(dev):
+        _lib.check(lib.dsv3_weight_quant(w.data_ptr(), N, K, q.data_ptr(), s.data_ptr(), _stream()))
+    return q, s
+
+
+def set_gemm_policy(kernel: int = KERNEL_AUTO, split_k: int = 0) -> None:
+    """Pin the fp8_gemm kernel / split-K factor (tests and benchmarks); (0, 0) restores automatic choice."""
+    _lib.check(lib.dsv3_set_gemm_policy(kernel, split_k))
+
+
+def check_device_status() -> None:
+    """Synchronise the current stream and raise if a kernel's bounded wait gave up."""
+    import ctypes
+    detail = (ctypes.c_uint32 * 4)()
+    rc = lib.dsv3_check_device_status(_stream(), ctypes.byref(detail))
+    if rc != _lib.OK:
+        for ws in _workspaces.values():   # tickets may be left non-zero by an aborted launch
+            ws[: _lib.WORKSPACE_HEADER_BYTES].zero_()
+        _lib.check(rc)

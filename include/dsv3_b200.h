@@ -1,0 +1,112 @@
+/*
+ * dsv3_b200 -- C ABI of the B200 (sm_100a) FP8 GEMM path for DeepSeek-V3 inference.
+ *
+ * Every entry point replaces one function of the reference's operator module
+ * `inference/kernel.py` (imported by `inference/model.py:10` and
+ * `inference/fp8_cast_bf16.py:10`) or a caller directly above it.  The reference
+ * binds these names in Python; a drop-in `kernel.py` that calls this library
+ * through ctypes is shipped next to it.
+ *
+ * Conventions
+ *   - plain device pointers and 64-bit sizes; no framework types;
+ *   - all tensors are row-major and contiguous, on the current CUDA device;
+ *   - work is enqueued on `stream` (a cudaStream_t) and the call returns without
+ *     synchronising; no entry point allocates device memory unless it says so;
+ *   - the return value is 0 on success or a negative DSV3_ERR_* code; a
+ *     human-readable detail of the last failure of the calling thread is
+ *     available from dsv3_last_error().
+ *   - e4m3 means float8_e4m3fn bytes; bf16 means bfloat16 bit patterns.
+ */
+#ifndef DSV3_B200_H_
+#define DSV3_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DSV3_OK 0
+#define DSV3_ERR_INVALID_ARGUMENT (-1)  /* null pointer, negative size, bad block size      */
+#define DSV3_ERR_UNSUPPORTED (-2)       /* shape or option the CUDA path does not implement */
+#define DSV3_ERR_CUDA (-3)              /* a CUDA runtime / driver call failed              */
+#define DSV3_ERR_WORKSPACE (-4)         /* workspace missing or too small                   */
+#define DSV3_ERR_DEVICE_TIMEOUT (-5)    /* a bounded device-side wait gave up               */
+
+#define DSV3_SCALE_FMT_FP32 0  /* scale_fmt=None  : s = amax/448                 (kernel.py:28)    */
+#define DSV3_SCALE_FMT_UE8M0 1 /* scale_fmt="ue8m0": s = 2^ceil(log2(amax/448))  (kernel.py:29-31) */
+
+typedef void* dsv3_stream_t; /* cudaStream_t */
+
+/* Library version: major*10000 + minor*100 + patch. */
+int dsv3_version(void);
+const char* dsv3_strerror(int status);
+const char* dsv3_last_error(void);
+
+/*
+ * act_quant -- replaces kernel.py:38-57 (kernel :9-35).
+ *   x : bf16 [rows, K], K % block_size == 0 (the reference asserts this, :52)
+ *   y : e4m3 [rows, K]           s : fp32 [rows, K / block_size]
+ * Per block of block_size consecutive elements: s = max(amax,1e-4)/448, y = e4m3(x/s),
+ * bit-identical to the reference kernel compiled for a GPU (approximate full-range
+ * division, round-to-nearest-even saturating cast).  block_size must be a multiple
+ * of 8 and at most 1024; 128 takes the tuned path.
+ */
+int dsv3_act_quant(const void* x, int64_t rows, int64_t K, int block_size, int scale_fmt,
+                   void* y, float* s, dsv3_stream_t stream);
+
+/*
+ * weight_dequant -- replaces kernel.py:89-110 (kernel :60-86).
+ *   w : e4m3 [N, K]   s : fp32 [ceil(N/block), ceil(K/block)]   y : bf16 [N, K]
+ *   y = bf16(float(w) * s[n / block, k / block])
+ */
+int dsv3_weight_dequant(const void* w, const float* s, int64_t N, int64_t K, int block_size,
+                        void* y, dsv3_stream_t stream);
+
+/*
+ * fp8_gemm -- replaces kernel.py:175-196 (kernel :118-172, tile configs :113-116).
+ *   a : e4m3 [M, K]   a_s : fp32 [M, ceil(K/128)]
+ *   b : e4m3 [N, K]   b_s : fp32 [ceil(N/128), ceil(K/128)]
+ *   c : bf16 [M, N]   c = sum over 128-wide K chunks of (a_chunk . b_chunk^T) * a_s * b_s,
+ *                     accumulated in fp32.
+ * `workspace` is scratch for the split-K variants: at least
+ * dsv3_fp8_gemm_workspace_bytes(M, N, K) bytes, 256-byte aligned, and its first
+ * DSV3_WORKSPACE_HEADER_BYTES must be zero before the first call (every call leaves
+ * them zero again).  One workspace must not be shared by calls that can overlap on
+ * the GPU.  It may be NULL when the size query returns 0.
+ */
+#define DSV3_WORKSPACE_HEADER_BYTES 16384
+size_t dsv3_fp8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int dsv3_fp8_gemm(const void* a, const float* a_s, const void* b, const float* b_s,
+                  int64_t M, int64_t N, int64_t K, void* c,
+                  void* workspace, size_t workspace_bytes, dsv3_stream_t stream);
+
+/*
+ * Kernel selection for fp8_gemm, for tests and benchmarks:
+ *   0 = automatic (default), 1 = CUDA-core tiled kernel (any shape),
+ *   2 = tcgen05 kernel, tokens on the MMA M axis, 3 = tcgen05 kernel, weights on the
+ *   MMA M axis (small M).  Values 2 and 3 fail with DSV3_ERR_UNSUPPORTED on shapes
+ *   those kernels cannot take.  split_k = 0 lets the library choose.
+ */
+int dsv3_set_gemm_policy(int kernel, int split_k);
+
+/*
+ * Harness weight quantiser (the reference ships only the inverse, weight_dequant;
+ * the checkpoint format is described in README_WEIGHTS.md:60-92).
+ *   w : bf16 [N, K] -> q : e4m3 [N, K], s : fp32 [ceil(N/128), ceil(K/128)]
+ *   per 128x128 block: s = max(amax,1e-4)/448 (IEEE division), q = e4m3(w / s).
+ */
+int dsv3_weight_quant(const void* w, int64_t N, int64_t K, void* q, float* s, dsv3_stream_t stream);
+
+/*
+ * Device status word.  Kernels with bounded waits record a give-up here instead of
+ * spinning forever.  Synchronises `stream`, returns DSV3_OK or DSV3_ERR_DEVICE_TIMEOUT
+ * and clears the word; `detail` (may be NULL) receives 4 words describing the wait.
+ */
+int dsv3_check_device_status(dsv3_stream_t stream, uint32_t detail[4]);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DSV3_B200_H_ */

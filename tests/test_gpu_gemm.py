@@ -1,0 +1,157 @@
+"""GPU parity of fp8_gemm (every kernel behind the C ABI) against the CPU oracle.
+
+Tolerance (stated by the task for this floating-point kernel): for every output element
+|y - y_ref| <= 1e-2 * (|y_ref| + rms(y_ref)) on the bf16 results.  At sizes the oracle
+cannot finish in seconds the check is size-independent: sampled token rows against the
+oracle (a GEMM row depends on nothing but that row of `a`), and the whole output against
+the CUDA-core kernel.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+from gpu_util import bf16_bits, assert_gemm_close
+
+pytestmark = pytest.mark.gpu
+
+AUTO, CORE, TC_TOKEN, TC_WEIGHT = 0, 1, 2, 3
+
+
+@pytest.fixture(scope="module")
+def K():
+    import kernel
+    torch.set_default_dtype(torch.bfloat16)
+    yield kernel
+    torch.set_default_dtype(torch.float32)
+
+
+@pytest.fixture(autouse=True)
+def _reset_policy():
+    import dsv3_b200
+    yield
+    dsv3_b200.set_gemm_policy(0, 0)
+    dsv3_b200.check_device_status()
+
+
+def run(K, policy, split, xq, xs, wq, ws):
+    import dsv3_b200
+    dsv3_b200.set_gemm_policy(policy, split)
+    y = K.fp8_gemm(xq.cuda(), xs.cuda(), wq.cuda(), ws.cuda())
+    dsv3_b200.check_device_status()
+    return y
+
+
+def quantised_case(M, N, Kd, seed):
+    x, _, wq, ws = O.make_case(M, N, Kd, seed)
+    kc = -(-Kd // 128)
+    if Kd % 128 == 0:
+        xq, xs = O.act_quant(x)
+    else:  # act_quant needs K % 128 == 0; quantise a zero-padded copy and crop (scales keep ceil(K/128) columns)
+        xp = torch.zeros(M, kc * 128, dtype=torch.bfloat16)
+        xp[:, :Kd] = x
+        xq, xs = O.act_quant(xp)
+        xq = xq.view(torch.uint8)[:, :Kd].contiguous().view(torch.float8_e4m3fn)
+    return xq, xs, wq, ws
+
+
+SMALL = [  # (M, N, K, seed)
+    (16, 2048, 1024, 0),     # BASELINE config 1
+    (1, 576, 7168, 2),       # wkv_a, decode
+    (3, 192, 256, 1),
+    (17, 64, 128, 21),
+    (8, 256, 192, 22),       # K tail (K % 128 = 64)
+    (33, 200, 384, 23),      # N not a multiple of 8
+    (64, 7168, 2048, 4),     # expert w2 at M = 64
+    (100, 576, 512, 24),     # partial tiles in both directions
+    (129, 130, 256, 25),
+    (256, 2048, 7168, 3),    # expert w1/w3 at M = 256
+]
+
+
+@pytest.mark.parametrize("policy,split", [(CORE, 0), (TC_TOKEN, 1), (TC_WEIGHT, 1), (TC_TOKEN, 2), (TC_WEIGHT, 3),
+                                          (AUTO, 0)],
+                         ids=["core", "tctoken", "tcweight", "tctoken_split2", "tcweight_split3", "auto"])
+@pytest.mark.parametrize("M,N,Kd,seed", SMALL)
+def test_fp8_gemm_vs_oracle(K, policy, split, M, N, Kd, seed):
+    xq, xs, wq, ws = quantised_case(M, N, Kd, seed)
+    ref = O.fp8_gemm(xq, xs, wq, ws)
+    y = run(K, policy, split, xq, xs, wq, ws)
+    assert y.shape == (M, N) and y.dtype == torch.bfloat16
+    assert_gemm_close(y, ref)
+
+
+def test_fp8_gemm_unaligned_k_uses_cuda_core_kernel(K):
+    xq, xs, wq, ws = quantised_case(5, 64, 100, 26)          # K % 16 != 0: no TMA descriptor possible
+    ref = O.fp8_gemm(xq, xs, wq, ws)
+    assert_gemm_close(run(K, AUTO, 0, xq, xs, wq, ws), ref)
+    import dsv3_b200
+    with pytest.raises(dsv3_b200.Dsv3Error, match="K % 16"):
+        run(K, TC_TOKEN, 1, xq, xs, wq, ws)
+
+
+def test_fp8_gemm_batched_leading_dims_and_empty(K):
+    xq, xs, wq, ws = quantised_case(12, 256, 256, 27)
+    ref = O.fp8_gemm(xq, xs, wq, ws)
+    y = K.fp8_gemm(xq.view(3, 4, 256).cuda(), xs.view(3, 4, 2).cuda(), wq.cuda(), ws.cuda())
+    assert y.shape == (3, 4, 256)
+    assert_gemm_close(y.view(12, 256), ref)
+    e = K.fp8_gemm(xq[:0].cuda(), xs[:0].cuda(), wq.cuda(), ws.cuda())
+    assert e.shape == (0, 256)
+
+
+def test_fp8_gemm_is_deterministic_with_split_k(K):
+    xq, xs, wq, ws = quantised_case(32, 1024, 4096, 28)
+    a = run(K, TC_WEIGHT, 4, xq, xs, wq, ws)
+    b = run(K, TC_WEIGHT, 4, xq, xs, wq, ws)
+    assert np.array_equal(bf16_bits(a), bf16_bits(b))
+
+
+def test_fp8_gemm_matches_gpu_reference_goldens(K, golden_gpu):
+    """Outputs of the reference's own Triton fp8_gemm on a B200, fed the reference's FP8 activations."""
+    for name, M, N, Kd, seed in [("cfg1", 16, 2048, 1024, 0), ("edge", 3, 192, 256, 1), ("wkv_a_m1", 1, 576, 7168, 2)]:
+        _, _, wq, ws = O.make_case(M, N, Kd, seed)
+        xq = torch.from_numpy(golden_gpu[f"{name}.act_quant.y"]).view(torch.float8_e4m3fn)
+        xs = torch.from_numpy(golden_gpu[f"{name}.act_quant.s"])
+        ref = torch.from_numpy(golden_gpu[f"{name}.fp8_gemm.c"].view(np.int16)).view(torch.bfloat16)
+        for policy in (AUTO, CORE):
+            assert_gemm_close(run(K, policy, 0, xq, xs, wq, ws), ref)
+
+
+FULL = [  # V3 shapes at sizes the oracle cannot cover whole: (M, N, K, seed)
+    (4096, 7168, 2048, 40),     # expert / shared w2, wo at TP=8
+    (4096, 576, 7168, 41),      # wkv_a
+    (1024, 24576, 1536, 42),    # wq_b
+    (2048, 4096, 512, 43),      # wkv_b slice
+    (16384, 2048, 7168, 44),    # expert w1/w3 at the largest M
+    (64, 18432, 7168, 45),      # dense w1/w3, decode
+    (8, 7168, 18432, 46),       # dense w2, decode
+]
+
+
+@pytest.mark.parametrize("M,N,Kd,seed", FULL)
+def test_fp8_gemm_full_size_properties(K, M, N, Kd, seed):
+    import dsv3_b200
+    x = O.randn_bf16((M, Kd), seed * 2 + 1, 1.0).cuda()
+    w = O.randn_bf16((N, Kd), seed * 2 + 2, 0.02).cuda()
+    wq, ws = dsv3_b200.weight_quant(w)
+    xq, xs = K.act_quant(x)
+    y = K.fp8_gemm(xq, xs, wq, ws)
+    dsv3_b200.check_device_status()
+    # (1) sampled rows against the oracle
+    g = np.random.Generator(np.random.PCG64(seed))
+    rows = sorted(set([0, 1, 127, 128, M - 1] + list(g.integers(0, M, 11))))
+    rows = [r for r in rows if r < M]
+    idx = torch.tensor(rows)
+    ref = O.fp8_gemm(xq[idx.cuda()].cpu().contiguous(), xs[idx.cuda()].cpu().contiguous(), wq.cpu(), ws.cpu())
+    assert_gemm_close(y[idx.cuda()], ref)
+    # (2) the whole output against the CUDA-core kernel (same inputs, independent code)
+    dsv3_b200.set_gemm_policy(CORE, 0)
+    y2 = K.fp8_gemm(xq, xs, wq, ws)
+    err = (y.float() - y2.float()).abs()
+    rms = y2.float().pow(2).mean().sqrt()
+    assert bool((err <= 1e-2 * (y2.float().abs() + rms)).all())
+    # (3) linearity in the activation scales: doubling a_s doubles the output exactly (power of two)
+    dsv3_b200.set_gemm_policy(AUTO, 0)
+    y3 = K.fp8_gemm(xq, xs * 2, wq, ws)
+    assert torch.equal(y3.float(), y.float() * 2)

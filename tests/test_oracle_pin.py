@@ -158,3 +158,51 @@ def test_weight_quant_round_trip_and_restatements():
     # e4m3 has 3 mantissa bits: relative error <= 2^-4 of the block amax
     blk = O._expand_block_scale(s, 300, 200, 128) * 448.0
     assert ((back - w.float()).abs() <= blk * 2 ** -4 + 1e-12).all()
+
+
+# ---------------------------------------------------------------------------------------
+# Second pin: outputs of the reference's Triton kernels compiled for and run on a B200
+# (tests/golden/ref_gpu_triton.npz, made by tests/golden/make_golden.py --device cuda).
+# ---------------------------------------------------------------------------------------
+GPU_CASES = CASES + [("expert_w13_m256", 256, 2048, 7168, 3), ("expert_w2_m64", 64, 7168, 2048, 4),
+                     ("wkv_a_m1024", 1024, 576, 7168, 5)]
+
+
+@pytest.mark.parametrize("name,M,N,K,seed", GPU_CASES)
+def test_oracle_vs_gpu_reference_act_quant(golden_gpu, name, M, N, K, seed):
+    from gpu_util import compare_act_quant_with_oracle
+    if f"{name}.act_quant.y" not in golden_gpu.files:
+        pytest.skip("only a digest is stored for this case")
+    x, _, _, _ = O.make_case(M, N, K, seed)
+    y = torch.from_numpy(golden_gpu[f"{name}.act_quant.y"]).view(torch.float8_e4m3fn)
+    s = torch.from_numpy(golden_gpu[f"{name}.act_quant.s"])
+    frac_s, frac_y = compare_act_quant_with_oracle(x, y, s)
+    assert frac_y < 0.01        # differences only at (near-)ties of the quotient
+
+
+@pytest.mark.parametrize("name,M,N,K,seed", GPU_CASES)
+def test_oracle_vs_gpu_reference_weight_dequant(golden_gpu, name, M, N, K, seed):
+    if N * K > (1 << 23):
+        pytest.skip("not stored")
+    _, _, wq, ws = O.make_case(1, N, K, seed)
+    assert sha(bf16_bits(O.weight_dequant(wq, ws))) == str(golden_gpu[f"{name}.weight_dequant.y.sha"])
+
+
+@pytest.mark.parametrize("name,M,N,K,seed", CASES)
+def test_oracle_vs_gpu_reference_fp8_gemm(golden_gpu, name, M, N, K, seed):
+    _, _, wq, ws = O.make_case(M, N, K, seed)
+    xq = torch.from_numpy(golden_gpu[f"{name}.act_quant.y"]).view(torch.float8_e4m3fn)
+    xs = torch.from_numpy(golden_gpu[f"{name}.act_quant.s"])
+    ref = torch.from_numpy(golden_gpu[f"{name}.fp8_gemm.c"].view(np.int16)).view(torch.bfloat16)
+    ok, ratio = O.gemm_tolerance_ok(O.fp8_gemm(xq, xs, wq, ws), ref)
+    assert ok, ratio
+
+
+def test_oracle_vs_gpu_reference_special(golden_gpu):
+    from gpu_util import compare_act_quant_with_oracle
+    x = torch.from_numpy(golden_gpu["special.in.x"].view(np.int16)).view(torch.bfloat16)
+    rows = [0, 1, 3, 4, 5, 6, 7]           # row 2 holds inf / overflow to inf
+    for tag, fmt in (("special", None), ("special_ue8m0", "ue8m0")):
+        y = torch.from_numpy(golden_gpu[f"{tag}.act_quant.y"]).view(torch.float8_e4m3fn)[rows].contiguous()
+        s = torch.from_numpy(golden_gpu[f"{tag}.act_quant.s"])[rows].contiguous()
+        compare_act_quant_with_oracle(x[rows].contiguous(), y, s, 128, fmt)
