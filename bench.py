@@ -8,7 +8,8 @@ One step = one pass of fp8_gemm over every (shape, M) pair of the sweep, M-major
 `value`  : aggregate fp8_gemm TFLOP/s with FP8 activations, weights and scales resident in HBM.
 `e2e`    : the same sweep through the drop-in module (`kernel.act_quant` + `kernel.fp8_gemm`) with the
            bf16 activations in pinned host memory and the bf16 results read back to the host, every step.
-`roofline`: the tcgen05 token-major kernel (launches with M >= 256), flops / CUDA-event time per launch.
+`roofline`: the tcgen05 token-major kernel (launches with M >= 256), flops / CUDA-event time of its launches
+           (each M column of the sweep is one CUDA graph, bracketed by events).
 `cpu_baseline` / `--impl reference`: the CPU restatement of the reference's kernel.py (oracle/) on the
            host cores, on a bounded sample of the sweep (the M = 64 column).
 
@@ -246,16 +247,12 @@ def run_ours(args):
     plan = [(name, K, N, M, ar) for M in MS for (name, K, N, _, ar) in rows]   # M-major
     total_flops = sum(gemm_flops(M, N, K) for _, K, N, M, _ in plan)
 
-    def one_step(events=None):
-        for name, K, N, M, ar in plan:
+    def column(M):
+        """fp8_gemm for every shape of the sweep at one M (one CUDA graph per column)."""
+        for name, K, N, _, ar in rows:
             _, xq, xs = acts[K]
             wq, ws = weights[name]
-            if events is not None:
-                e0 = torch.cuda.Event(enable_timing=True); e0.record()
             y = kernel.fp8_gemm(xq[:M], xs[:M], wq, ws)
-            if events is not None:
-                e1 = torch.cuda.Event(enable_timing=True); e1.record()
-                events.append((name, K, N, M, e0, e1))
             if ar:
                 dist.all_reduce(y)
 
@@ -264,21 +261,43 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 3)):
-        one_step()
-    dsv3_b200.check_device_status()
+    # The decode-sized launches last a few microseconds, less than the host needs to issue one, so
+    # each M column is captured once into a CUDA graph and a step replays the eight graphs: the GPU
+    # then runs the launches back to back.  Capture happens on the stream the warm-up ran on so the
+    # split-K workspace of that stream already exists.
+    side = torch.cuda.Stream(device=dev)
+    graphs = {}
+    with torch.cuda.stream(side):
+        for _ in range(max(args.warmup, 3)):
+            for M in MS:
+                column(M)
+        dsv3_b200.check_device_status()
+        for M in MS:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                column(M)
+            graphs[M] = g
+        for M in MS:
+            graphs[M].replay()
+    barrier()
 
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
     # ---- timed region 1: resident inputs ----------------------------------------------
-    events = []
+    col_events = []
     barrier()
-    t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
-    t0.record()
-    for _ in range(args.steps):
-        one_step(events)
-    t1.record()
+    with torch.cuda.stream(side):
+        t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(args.steps):
+            marks = [torch.cuda.Event(enable_timing=True) for _ in range(len(MS) + 1)]
+            marks[0].record()
+            for i, M in enumerate(MS):          # M-major: every weight is used once per column
+                graphs[M].replay()
+                marks[i + 1].record()
+            col_events.append(marks)
+        t1.record()
     barrier()
     ms = t0.elapsed_time(t1)
     if world > 1:
@@ -320,19 +339,21 @@ def run_ours(args):
     dsv3_b200.check_device_status()
     clocks = sampler.stop() if rank == 0 else None
 
-    # ---- per-kernel roofline from the per-launch events of region 1 -------------------
+    # ---- per-kernel roofline from the per-column events of region 1 -------------------
     big_t = big_f = small_t = small_b = 0.0
     n_big = n_small = 0
-    per_shape = {}
-    for name, K, N, M, e0, e1 in events:
-        dt = e0.elapsed_time(e1) * 1e-3
-        key = f"{name}@M={M}"
-        acc = per_shape.setdefault(key, [0.0, 0, gemm_flops(M, N, K), gemm_bytes(M, N, K)])
-        acc[0] += dt; acc[1] += 1
-        if M >= 256:
-            big_t += dt; big_f += gemm_flops(M, N, K); n_big += 1
-        elif M <= 64:
-            small_t += dt; small_b += gemm_bytes(M, N, K); n_small += 1
+    per_column = {}
+    for marks in col_events:
+        for i, M in enumerate(MS):
+            dt = marks[i].elapsed_time(marks[i + 1]) * 1e-3
+            fl = sum(gemm_flops(M, N, K) for _, K, N, _, _ in rows)
+            by = sum(gemm_bytes(M, N, K) for _, K, N, _, _ in rows)
+            acc = per_column.setdefault(M, [0.0, 0, fl, by])
+            acc[0] += dt; acc[1] += 1
+            if M >= 256:
+                big_t += dt; big_f += fl; n_big += len(rows)
+            elif M <= 64:
+                small_t += dt; small_b += by; n_small += len(rows)
     fp8_peak = 2.0 * peaks["bf16_tflops_sustained"]
     roofline = {
         "kernel": "fp8_gemm_tc_kernel<128,false> (tcgen05, token-major tiles; launches with M >= 256)",
@@ -349,8 +370,8 @@ def run_ours(args):
         "peak_source": f"hbm_gbs of MEASURED_PEAKS.json ({peaks['source']})",
         "launches": n_small, "algorithmic": "M*K + N*K + scales + 2*M*N bytes per launch",
     }
-    detail = {k: {"us": v[0] / v[1] * 1e6, "tflops": v[2] / (v[0] / v[1]) / 1e12, "gbs": v[3] / (v[0] / v[1]) / 1e9}
-              for k, v in per_shape.items()}
+    detail = {f"M={k}": {"us_per_column": v[0] / v[1] * 1e6, "tflops": v[2] / (v[0] / v[1]) / 1e12,
+                         "gbs": v[3] / (v[0] / v[1]) / 1e9, "launches": len(rows)} for k, v in per_column.items()}
 
     if world > 1:
         dist.barrier()
@@ -381,11 +402,99 @@ def run_ours(args):
                 "path": "pinned host bf16 activations -> kernel.act_quant -> kernel.fp8_gemm -> bf16 result to pinned host; "
                         "weights resident on the device"},
         "gpu_launches": len(plan) * args.steps, "gpu_launches_e2e": 2 * len(plan) * args.steps,
-        "clocks": clocks, "per_shape": detail,
+        "clocks": clocks, "per_column": detail,
     }
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def run_single(args):
+    """One (M, N, K) problem, `steps` launches of act_quant / fp8_gemm / weight_dequant: the small case
+    the ncu captures under profiles/ are taken on.  Prints per-launch CUDA-event times."""
+    import torch
+    import dsv3_b200
+    import kernel
+    M, N, K = (int(v) for v in args.single.split(","))
+    torch.cuda.set_device(0)
+    torch.set_default_dtype(torch.bfloat16)
+    torch.manual_seed(0)
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    wq, ws = dsv3_b200.weight_quant((torch.randn(N, K, device="cuda") * 0.02).to(torch.bfloat16))
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    out = {"M": M, "N": N, "K": K}
+    for name, fn in (("act_quant", lambda: kernel.act_quant(x)), ("fp8_gemm", None),
+                     ("weight_dequant", lambda: kernel.weight_dequant(wq, ws))):
+        if fn is None:
+            xq, xs = kernel.act_quant(x)
+            fn = lambda: kernel.fp8_gemm(xq, xs, wq, ws)
+        ts = []
+        for i in range(args.warmup + args.steps):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record(); fn(); e1.record()
+            torch.cuda.synchronize()
+            if i >= args.warmup:
+                ts.append(e0.elapsed_time(e1) * 1e3)
+        out[name + "_us"] = sorted(ts)[len(ts) // 2]
+    dsv3_b200.check_device_status()
+    out["fp8_gemm_tflops"] = gemm_flops(M, N, K) / out["fp8_gemm_us"] / 1e6
+    out["fp8_gemm_gbs"] = gemm_bytes(M, N, K) / out["fp8_gemm_us"] / 1e3
+    print(json.dumps(out), flush=True)
+
+
+def run_detail(args):
+    """Per-(shape, M) table: every problem of the sweep timed alone.  A CUDA graph holds R launches
+    over R distinct weight copies (R x weight bytes >= 256 MB, more than L2), so launches run back to
+    back on weights that are not cache-resident.  Prints one JSON line per problem."""
+    import torch
+    import dsv3_b200
+    import kernel
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    torch.set_default_dtype(torch.bfloat16)
+    torch.manual_seed(7)
+    peaks = read_peaks()
+    fp8_peak = 2.0 * peaks["bf16_tflops_sustained"]
+    rows = sweep_rows(1)
+    ms_list = [int(v) for v in args.detail_m.split(",")] if args.detail_m else MS
+    side = torch.cuda.Stream(device=dev)
+    out = []
+    for name, K, N, _, _ in rows:
+        R = max(2, min(64, -(-(256 << 20) // (N * K))))
+        w = (torch.randn(N, K, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+        wq0, ws0 = dsv3_b200.weight_quant(w)
+        del w
+        copies = [(wq0.clone(), ws0.clone()) for _ in range(R)]
+        for M in ms_list:
+            x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+            xq, xs = kernel.act_quant(x)
+            with torch.cuda.stream(side):
+                for wq, ws in copies[:2]:
+                    kernel.fp8_gemm(xq, xs, wq, ws)
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    for wq, ws in copies:
+                        kernel.fp8_gemm(xq, xs, wq, ws)
+                g.replay()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(args.steps):
+                    g.replay()
+                e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / (args.steps * R)
+            tf, gb = gemm_flops(M, N, K) / us / 1e6, gemm_bytes(M, N, K) / us / 1e3
+            t_roof = max(gemm_flops(M, N, K) / (fp8_peak * 1e12), gemm_bytes(M, N, K) / (peaks["hbm_gbs"] * 1e9)) * 1e6
+            r = {"shape": name, "K": K, "N": N, "M": M, "us": round(us, 2), "tflops": round(tf, 1), "gbs": round(gb, 0),
+                 "roofline_us": round(t_roof, 2), "frac_of_roofline": round(t_roof / us, 3),
+                 "bound": "tensor" if gemm_flops(M, N, K) / (fp8_peak * 1e12) > gemm_bytes(M, N, K) / (peaks["hbm_gbs"] * 1e9) else "hbm"}
+            out.append(r)
+            print(json.dumps(r), flush=True)
+            del g
+        del copies
+    dsv3_b200.check_device_status()
 
 
 def main():
@@ -395,8 +504,16 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--single", default=None, metavar="M,N,K",
+                    help="run one problem instead of the sweep (the case ncu captures are taken on)")
+    ap.add_argument("--detail", action="store_true", help="per-(shape, M) table instead of the aggregate sweep")
+    ap.add_argument("--detail-m", default=None, metavar="M1,M2,...", help="restrict --detail to these M values")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.single:
+        run_single(args)
+    elif args.detail:
+        run_detail(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

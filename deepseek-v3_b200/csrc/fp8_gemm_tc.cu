@@ -14,7 +14,8 @@
 //   warp 0 (1 lane)  TMA producer : waits empty[g % NS], loads the P and Q tiles of chunk g
 //   warp 1 (1 lane)  MMA issuer   : waits full[g % NS] and tempty[g % NT], issues 4 MMAs,
 //                                   commits to empty[g % NS] and tfull[g % NT]
-//   warps 4..11      promotion    : wait tfull[g % NT], tcgen05.ld, release tempty, FMA;
+//   warps 4..11      promotion    : wait tfull[g % NT], tcgen05.ld, release tempty, FMA (the load of
+//                                   chunk g+1 is issued before the FMAs of chunk g);
 //                                   at the end of a work item write C (or a split-K partial)
 // Operand roles: P is the 128-row MMA "A" operand, Q the BN-row MMA "B" operand.
 //   kSwap = false : P = 128 tokens of a,  Q = 128 rows of b  (large M)
@@ -36,8 +37,10 @@ namespace dsv3 {
 
 namespace {
 
-constexpr int kNumThreads = 384;          // warps 0..3: producer, MMA, 2 spare; warps 4..11: promotion
+constexpr int kNumThreads = 384;          // warp 0: TMA producer, warp 1: MMA issuer, 2-3 idle, 4..11: promotion
 constexpr int kPromoThreads = 256;
+constexpr int kFirstPromoWarp = 4;
+
 constexpr int kPRows = 128;               // MMA M
 constexpr int kChunk = 128;               // K elements (= bytes) per chunk
 constexpr int kTmemStages = 4;
@@ -233,28 +236,55 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
                 }
             }
         }
-    } else if (warp >= 4) {
+    } else if (warp >= kFirstPromoWarp) {
         // ------------------------------------------------------------ promotion + epilogue
-        const int pw = warp - 4;
-        const int quarter = warp & 3;           // TMEM lane quarter this warp may access
-        const int half = pw >> 2;               // which half of the BN columns
-        const int row = quarter * 32 + lane;    // accumulator row (TMEM lane)
+        const int quarter = warp & 3;                       // TMEM lane quarter this warp may access
+        const int half = (warp - kFirstPromoWarp) >> 2;     // which half of the BN columns
+        const int row = quarter * 32 + lane;                // accumulator row (TMEM lane)
         const int col0 = half * CPT;
         const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + col0;
         const int64_t M = p.M, N = p.N;
         const int kc = p.kc;
         uint32_t g = 0;
         bool ok = true;
+
+        // A chunk is read back in SPC steps of HC columns (two steps of 32 for the 64-column case)
+        // so that one step's TMEM load is in flight while the previous step's FMAs issue.
+        constexpr int HC = (CPT == 64) ? 32 : CPT;
+        constexpr int SPC = CPT / HC;
+        // Issues (does not wait for) the load of step `st` of chunk `gg`; the first step of a chunk
+        // first waits for the chunk's product to be complete in TMEM.
+        auto issue_load = [&](uint32_t gg, int st, uint32_t* v) -> bool {
+            const int ts = gg % NT;
+            if (st == 0) {
+                const bool mine = bounded_wait(tfull_bar(ts), (gg / NT) & 1u, ctl, p.status, 4, gg);
+                if (!__all_sync(0xffffffffu, mine)) return false;
+                tc_fence_after();
+            }
+            tmem_load_cols<HC>(t_lane + ts * BN + st * HC, v);
+            return true;
+        };
+        // Completes the outstanding load; after the last step of a chunk the TMEM stage goes back
+        // to the MMA issuer.
+        auto finish_load = [&](uint32_t gg, int st) {
+            tc_wait_ld();
+            if (st == SPC - 1) {
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tempty_bar(gg % NT));
+            }
+        };
+
         for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
             const Item it = decode_item(item, p);
-            float acc[CPT];
+            float2 acc[CPT / 2];
 #pragma unroll
-            for (int j = 0; j < CPT; ++j) acc[j] = 0.0f;
+            for (int j = 0; j < CPT / 2; ++j) acc[j] = make_float2(0.0f, 0.0f);
 
             // token / weight-row coordinates of this thread
             const int64_t p_row = static_cast<int64_t>(it.p_idx) * kPRows + row;
             const int64_t q_base = static_cast<int64_t>(it.q_idx) * BN + col0;
-            const float* as_ptr;  // normal: this row's scales ; swap: scales of token q_base
+            const float* as_ptr;  // normal: this row's scales ; swap: scale matrix, indexed per token below
             const float* bs_ptr;
             if constexpr (!kSwap) {
                 as_ptr = p.a_s + min(p_row, M - 1) * kc;
@@ -263,38 +293,71 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
                 as_ptr = p.a_s;
                 bs_ptr = p.b_s + static_cast<int64_t>(it.p_idx) * kc;          // 128 weight rows = one scale row
             }
-
-            for (int ch = it.c0; ch < it.c1; ++ch, ++g) {
-                const int ts = g % NT;
-                float sc[kSwap ? CPT : 1];
-                const float bs = __ldg(bs_ptr + ch);
+            // scale of chunk ch for this thread's row (token-major tiles); index clamped so that the
+            // look-ahead below never leaves the item's chunk range
+            auto row_scale = [&](int ch) -> float {
+                const int c = min(ch, it.c1 - 1);
+                return __ldg(as_ptr + c) * __ldg(bs_ptr + c);
+            };
+            // acc[off ..] += v * (a_s * b_s) for chunk ch; v holds HC columns starting at column 2*off
+            auto fold = [&](int ch, const uint32_t* v, float sc, int off) {
                 if constexpr (!kSwap) {
-                    sc[0] = __ldg(as_ptr + ch) * bs;
-                } else {
+                    const float2 sc2 = make_float2(sc, sc);
 #pragma unroll
-                    for (int j = 0; j < CPT; ++j) {
-                        const int64_t m = min(q_base + j, M - 1);
-                        sc[j] = __ldg(as_ptr + m * kc + ch) * bs;
+                    for (int j = 0; j < HC / 2; ++j)
+                        acc[off + j] = __ffma2_rn(make_float2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1])),
+                                                  sc2, acc[off + j]);
+                } else {
+                    const float bs = __ldg(bs_ptr + ch);
+#pragma unroll
+                    for (int j = 0; j < HC / 2; ++j) {
+                        const int64_t m0 = min(q_base + 2 * j, M - 1), m1 = min(q_base + 2 * j + 1, M - 1);
+                        const float2 sc2 = make_float2(__ldg(as_ptr + m0 * kc + ch) * bs, __ldg(as_ptr + m1 * kc + ch) * bs);
+                        acc[off + j] = __ffma2_rn(make_float2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1])),
+                                                  sc2, acc[off + j]);
                     }
                 }
-                bool mine = bounded_wait(tfull_bar(ts), (g / NT) & 1u, ctl, p.status, 4, g);
-                ok = __all_sync(0xffffffffu, mine);
-                if (!ok) break;
-                tc_fence_after();
-                uint32_t v[CPT];
-                tmem_load_cols<CPT>(t_lane + ts * BN, v);
-                tc_wait_ld();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(tempty_bar(ts));
-#pragma unroll
-                for (int j = 0; j < CPT; ++j) acc[j] = fmaf(__uint_as_float(v[j]), sc[kSwap ? j : 0], acc[j]);
+            };
+
+            // Software pipeline over the load steps of this item, two register buffers.  The loop body
+            // covers two steps: one chunk when SPC == 2, two chunks when SPC == 1.  Row scales
+            // (global memory) are fetched two chunks ahead of their use.
+            const int n_ch = it.c1 - it.c0;
+            const int n_steps = n_ch * SPC;
+            uint32_t va[HC], vb[HC];
+            float s0 = 0.0f, s1 = 0.0f;
+            if constexpr (!kSwap) {
+                s0 = row_scale(it.c0);
+                s1 = row_scale(it.c0 + 1);
             }
+            ok = issue_load(g, 0, va);
+            for (int t = 0; ok && t < n_steps; t += 2) {
+                const int ca = t / SPC, cb = (t + 1) / SPC, cc = (t + 2) / SPC;   // chunk of steps t, t+1, t+2
+                float s2 = 0.0f;
+                finish_load(g + ca, t % SPC);
+                if (t + 1 < n_steps) ok = issue_load(g + cb, (t + 1) % SPC, vb);
+                if constexpr (!kSwap) s2 = row_scale(it.c0 + ca + 2);
+                fold(it.c0 + ca, va, s0, 0);
+                if (ok && t + 1 < n_steps) {
+                    finish_load(g + cb, (t + 1) % SPC);
+                    if (t + 2 < n_steps) ok = issue_load(g + cc, (t + 2) % SPC, va);
+                    fold(it.c0 + cb, vb, SPC == 2 ? s0 : s1, SPC == 2 ? HC / 2 : 0);
+                }
+                if constexpr (SPC == 2) {
+                    s0 = s1;
+                    s1 = s2;
+                } else if constexpr (!kSwap) {
+                    s0 = s2;   // unreachable today (token-major tiles always have SPC == 2); kept consistent
+                    s1 = row_scale(it.c0 + ca + 3);
+                }
+            }
+            g += n_ch;
             if (!ok) break;
 
             // ---------------------------------------------------- write-out
             // normal: thread = token row, CPT consecutive output columns
             // swap  : thread = output column (weight row), CPT tokens
+            const float* accf = reinterpret_cast<const float*>(acc);
             if (p.splits == 1) {
                 if constexpr (!kSwap) {
                     if (p_row < M) {
@@ -304,13 +367,13 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
                         for (int j = 0; j < CPT; j += 8) {
                             const int64_t n = q_base + j;
                             if (vec_ok && n + 8 <= N) {
-                                uint4 o = make_uint4(pack_bf16x2(acc[j], acc[j + 1]), pack_bf16x2(acc[j + 2], acc[j + 3]),
-                                                     pack_bf16x2(acc[j + 4], acc[j + 5]), pack_bf16x2(acc[j + 6], acc[j + 7]));
+                                uint4 o = make_uint4(pack_bf16x2(accf[j], accf[j + 1]), pack_bf16x2(accf[j + 2], accf[j + 3]),
+                                                     pack_bf16x2(accf[j + 4], accf[j + 5]), pack_bf16x2(accf[j + 6], accf[j + 7]));
                                 *reinterpret_cast<uint4*>(crow + n) = o;
                             } else {
 #pragma unroll
                                 for (int e = 0; e < 8; ++e)
-                                    if (n + e < N) crow[n + e] = __float2bfloat16_rn(acc[j + e]);
+                                    if (n + e < N) crow[n + e] = __float2bfloat16_rn(accf[j + e]);
                             }
                         }
                     }
@@ -319,18 +382,27 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
 #pragma unroll
                         for (int j = 0; j < CPT; ++j) {
                             const int64_t m = q_base + j;
-                            if (m < M) p.c[m * N + p_row] = __float2bfloat16_rn(acc[j]);
+                            if (m < M) p.c[m * N + p_row] = __float2bfloat16_rn(accf[j]);
                         }
                     }
                 }
             } else {
+                // split-K: park the partial sums, take a ticket, the last arrival of the tile reduces
                 float* part = p.partials + static_cast<int64_t>(it.split) * M * N;
+                const bool vec4 = (N % 4) == 0;
                 if constexpr (!kSwap) {
                     if (p_row < M) {
 #pragma unroll
-                        for (int j = 0; j < CPT; ++j) {
+                        for (int j = 0; j < CPT; j += 4) {
                             const int64_t n = q_base + j;
-                            if (n < N) __stcg(part + p_row * N + n, acc[j]);
+                            if (vec4 && n + 4 <= N) {
+                                __stcg(reinterpret_cast<float4*>(part + p_row * N + n),
+                                       make_float4(accf[j], accf[j + 1], accf[j + 2], accf[j + 3]));
+                            } else {
+#pragma unroll
+                                for (int e = 0; e < 4; ++e)
+                                    if (n + e < N) __stcg(part + p_row * N + n + e, accf[j + e]);
+                            }
                         }
                     }
                 } else {
@@ -338,13 +410,13 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
 #pragma unroll
                         for (int j = 0; j < CPT; ++j) {
                             const int64_t m = q_base + j;
-                            if (m < M) __stcg(part + m * N + p_row, acc[j]);
+                            if (m < M) __stcg(part + m * N + p_row, accf[j]);
                         }
                     }
                 }
                 __threadfence();
                 promo_barrier();
-                if (threadIdx.x == 4 * 32) {
+                if (threadIdx.x == kFirstPromoWarp * 32) {
                     const int t = atomicAdd(p.tickets + it.tile, 1);
                     if (t == p.splits - 1) p.tickets[it.tile] = 0;  // last arrival: leave the ticket clean
                     ctl->ticket = t;
@@ -354,17 +426,43 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
                 promo_barrier();  // everyone has read the ticket before the next item overwrites it
                 if (last) {
                     __threadfence();
+                    // sum in split order (deterministic); every trip keeps CPT independent loads in flight
+                    float sum[CPT];
+#pragma unroll
+                    for (int j = 0; j < CPT; ++j) sum[j] = 0.0f;
+                    for (int s = 0; s < p.splits; ++s) {
+                        const float* ps = p.partials + static_cast<int64_t>(s) * M * N;
+                        if constexpr (!kSwap) {
+                            if (p_row < M) {
+#pragma unroll
+                                for (int j = 0; j < CPT; j += 4) {
+                                    const int64_t n = q_base + j;
+                                    if (vec4 && n + 4 <= N) {
+                                        const float4 t4 = __ldcg(reinterpret_cast<const float4*>(ps + p_row * N + n));
+                                        sum[j] += t4.x; sum[j + 1] += t4.y; sum[j + 2] += t4.z; sum[j + 3] += t4.w;
+                                    } else {
+#pragma unroll
+                                        for (int e = 0; e < 4; ++e)
+                                            if (n + e < N) sum[j + e] += __ldcg(ps + p_row * N + n + e);
+                                    }
+                                }
+                            }
+                        } else {
+                            if (p_row < N) {
+#pragma unroll
+                                for (int j = 0; j < CPT; ++j) {
+                                    const int64_t m = q_base + j;
+                                    if (m < M) sum[j] += __ldcg(ps + m * N + p_row);
+                                }
+                            }
+                        }
+                    }
                     if constexpr (!kSwap) {
                         if (p_row < M) {
 #pragma unroll
                             for (int j = 0; j < CPT; ++j) {
                                 const int64_t n = q_base + j;
-                                if (n < N) {
-                                    float sum = 0.0f;
-                                    for (int s = 0; s < p.splits; ++s)
-                                        sum += __ldcg(p.partials + (static_cast<int64_t>(s) * M + p_row) * N + n);
-                                    p.c[p_row * N + n] = __float2bfloat16_rn(sum);
-                                }
+                                if (n < N) p.c[p_row * N + n] = __float2bfloat16_rn(sum[j]);
                             }
                         }
                     } else {
@@ -372,12 +470,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
 #pragma unroll
                             for (int j = 0; j < CPT; ++j) {
                                 const int64_t m = q_base + j;
-                                if (m < M) {
-                                    float sum = 0.0f;
-                                    for (int s = 0; s < p.splits; ++s)
-                                        sum += __ldcg(p.partials + (static_cast<int64_t>(s) * M + m) * N + p_row);
-                                    p.c[m * N + p_row] = __float2bfloat16_rn(sum);
-                                }
+                                if (m < M) p.c[m * N + p_row] = __float2bfloat16_rn(sum[j]);
                             }
                         }
                     }

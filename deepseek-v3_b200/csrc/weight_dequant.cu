@@ -25,20 +25,22 @@ __device__ __forceinline__ uint4 dequant8(uint32_t lo, uint32_t hi, float s) {
 }
 
 // K % 16 == 0: a 16-element group never straddles a scale block (block % 16 == 0).
+// Index is uint32_t when the group count fits (64-bit division per group would make the
+// kernel instruction-bound), int64_t otherwise.
+template <typename Index>
 __global__ void __launch_bounds__(kThreads) weight_dequant_vec_kernel(const uint4* __restrict__ w,
                                                                        const float* __restrict__ s,
-                                                                       uint4* __restrict__ y, int64_t N, int64_t K,
-                                                                       int block, int64_t kb) {
-    const int64_t groups_per_row = K >> 4;
-    const int64_t total = N * groups_per_row;
-    const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
-    for (int64_t g = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; g < total; g += stride) {
-        const int64_t n = g / groups_per_row;
-        const int64_t k = (g - n * groups_per_row) << 4;
-        const float sc = __ldg(s + (n / block) * kb + (k / block));
+                                                                       uint4* __restrict__ y, Index total,
+                                                                       Index groups_per_row, Index block,
+                                                                       Index kb) {
+    const Index stride = static_cast<Index>(gridDim.x) * kThreads;
+    for (Index g = static_cast<Index>(blockIdx.x) * kThreads + threadIdx.x; g < total; g += stride) {
+        const Index n = g / groups_per_row;
+        const Index k = (g - n * groups_per_row) << 4;
+        const float sc = __ldg(s + static_cast<size_t>(n / block) * kb + (k / block));
         const uint4 v = __ldcs(w + g);
-        __stcs(y + 2 * g, dequant8(v.x, v.y, sc));
-        __stcs(y + 2 * g + 1, dequant8(v.z, v.w, sc));
+        __stcs(y + 2 * static_cast<size_t>(g), dequant8(v.x, v.y, sc));
+        __stcs(y + 2 * static_cast<size_t>(g) + 1, dequant8(v.z, v.w, sc));
     }
 }
 
@@ -98,8 +100,14 @@ int launch_weight_dequant(const void* w, const float* s, int64_t N, int64_t K, i
         const int64_t total = N * (K >> 4);
         int64_t grid = (total + kThreads - 1) / kThreads;
         if (grid > cap) grid = cap;
-        weight_dequant_vec_kernel<<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
-            static_cast<const uint4*>(w), s, static_cast<uint4*>(y), N, K, block, kb);
+        if (total < (1ll << 31) && kb < (1ll << 31)) {
+            weight_dequant_vec_kernel<uint32_t><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
+                static_cast<const uint4*>(w), s, static_cast<uint4*>(y), static_cast<uint32_t>(total),
+                static_cast<uint32_t>(K >> 4), static_cast<uint32_t>(block), static_cast<uint32_t>(kb));
+        } else {
+            weight_dequant_vec_kernel<int64_t><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
+                static_cast<const uint4*>(w), s, static_cast<uint4*>(y), total, K >> 4, static_cast<int64_t>(block), kb);
+        }
     } else {
         int64_t grid = (N * K + kThreads - 1) / kThreads;
         if (grid > cap) grid = cap;

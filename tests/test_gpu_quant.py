@@ -139,7 +139,7 @@ def test_weight_dequant_other_block_and_empty(K):
     y = K.weight_dequant(wq.cuda(), s.cuda(), 32)
     assert np.array_equal(bf16_bits(y), bf16_bits(O.weight_dequant(wq, s, 32)))
     e = K.weight_dequant(torch.empty(0, 128, dtype=torch.float8_e4m3fn, device="cuda"),
-                         torch.empty(0, 1, device="cuda"))
+                         torch.empty(0, 1, dtype=torch.float32, device="cuda"))
     assert e.shape == (0, 128)
 
 
