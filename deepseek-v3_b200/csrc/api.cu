@@ -4,6 +4,7 @@
 #include <cstring>
 
 #include "common.cuh"
+#include "gemm_plan.cuh"
 
 namespace dsv3 {
 
@@ -14,18 +15,6 @@ int launch_weight_dequant(const void* w, const float* s, int64_t N, int64_t K, i
 int launch_weight_quant(const void* w, int64_t N, int64_t K, void* q, float* s, cudaStream_t stream);
 int launch_fp8_gemm_simple(const void* a, const float* a_s, const void* b, const float* b_s, int64_t M, int64_t N,
                            int64_t K, void* c, cudaStream_t stream);
-
-struct TcPlan {
-    bool swap;
-    int bn;
-    int tiles_p, tiles_q, splits, kc;
-};
-bool tc_supported(const void* a, const void* b, const void* c, int64_t M, int64_t N, int64_t K);
-TcPlan tc_plan(int64_t M, int64_t N, int64_t K, int force_kernel, int force_split);
-size_t tc_workspace_bytes(const TcPlan& pl, int64_t M, int64_t N);
-int launch_fp8_gemm_tc(const void* a, const float* a_s, const void* b, const float* b_s, int64_t M, int64_t N,
-                       int64_t K, void* c, void* workspace, size_t workspace_bytes, const TcPlan& pl,
-                       cudaStream_t stream);
 
 // ------------------------------------------------------------------ errors
 static thread_local char t_last_error[512] = "";
@@ -78,6 +67,8 @@ unsigned int* status_device_ptr() {
 
 static int g_force_kernel = 0;
 static int g_force_split = 0;
+int gemm_policy_kernel() { return g_force_kernel; }
+int gemm_policy_split() { return g_force_split; }
 
 static bool is_null(const void* p) { return p == nullptr; }
 

@@ -32,6 +32,7 @@
 #include <unordered_map>
 
 #include "common.cuh"
+#include "gemm_plan.cuh"
 
 namespace dsv3 {
 
@@ -555,13 +556,6 @@ int launch_variant(const CUtensorMap& tp, const CUtensorMap& tq, const TcParams&
 }
 
 }  // namespace
-
-// Geometry chosen for a problem; shared by the workspace query and the launch.
-struct TcPlan {
-    bool swap;
-    int bn;
-    int tiles_p, tiles_q, splits, kc;
-};
 
 bool tc_supported(const void* a, const void* b, const void* c, int64_t M, int64_t N, int64_t K) {
     return M > 0 && N > 0 && K >= 16 && (K % 16) == 0 && (reinterpret_cast<uintptr_t>(a) % 16) == 0 &&

@@ -23,7 +23,7 @@ WORKSPACE_HEADER_BYTES = 16384
 EXPORTS = (
     "dsv3_version", "dsv3_strerror", "dsv3_last_error", "dsv3_act_quant", "dsv3_weight_dequant",
     "dsv3_fp8_gemm_workspace_bytes", "dsv3_fp8_gemm", "dsv3_set_gemm_policy", "dsv3_weight_quant",
-    "dsv3_check_device_status",
+    "dsv3_check_device_status", "dsv3_fp8_gemm_static", "dsv3_fp8_gemm_static_scratch_bytes",
 )
 
 
@@ -49,6 +49,9 @@ def _load() -> ctypes.CDLL:
     lib.dsv3_fp8_gemm_workspace_bytes.argtypes = [i64, i64, i64]
     lib.dsv3_fp8_gemm_workspace_bytes.restype = sz
     lib.dsv3_fp8_gemm.argtypes = [vp, vp, vp, vp, i64, i64, i64, vp, vp, sz, vp]
+    lib.dsv3_fp8_gemm_static.argtypes = [vp, vp, vp, vp, i64, i64, i64, vp, vp]
+    lib.dsv3_fp8_gemm_static.restype = ci
+    lib.dsv3_fp8_gemm_static_scratch_bytes.restype = sz
     lib.dsv3_set_gemm_policy.argtypes = [ci, ci]
     lib.dsv3_weight_quant.argtypes = [vp, i64, i64, vp, vp, vp]
     lib.dsv3_check_device_status.argtypes = [vp, ctypes.POINTER(ctypes.c_uint32 * 4)]

@@ -83,6 +83,26 @@ int dsv3_fp8_gemm(const void* a, const float* a_s, const void* b, const float* b
                   void* workspace, size_t workspace_bytes, dsv3_stream_t stream);
 
 /*
+ * fp8_gemm for hosts that have no device memory to lend -- no counterpart in the reference, whose
+ * Python wrapper simply lets torch allocate.  Same arithmetic and the same kernels as dsv3_fp8_gemm,
+ * but the split-K scratch is a fixed array of DSV3_STATIC_SCRATCH_BYTES inside the library image, so the
+ * call performs no device allocation of any kind.  Meant for a process that committed all device
+ * memory to its own arena at start-up (an allocation in the request path would fail, or would stall all
+ * streams while the driver synchronises), and for C programs with no framework allocator to borrow from.
+ *   - Every GPU that loads the library carries the array until the process exits.
+ *   - Problems whose split-K plan needs more scratch than that are refused with DSV3_ERR_WORKSPACE;
+ *     shapes the tcgen05 kernels cannot take (K % 16 != 0, unaligned pointers) with DSV3_ERR_UNSUPPORTED.
+ *   - The first call on a device looks up the array's device address (that device must be current); make
+ *     that first call before starting any stream capture.
+ *   - All calls on a device share the array: calls that can overlap on the GPU race on it.  The part that
+ *     must start at zero is cleared on `stream` ahead of each launch.
+ */
+#define DSV3_STATIC_SCRATCH_BYTES (16384 + (8u << 20))
+size_t dsv3_fp8_gemm_static_scratch_bytes(void);
+int dsv3_fp8_gemm_static(const void* a, const float* a_s, const void* b, const float* b_s,
+                         int64_t M, int64_t N, int64_t K, void* c, dsv3_stream_t stream);
+
+/*
  * Kernel selection for fp8_gemm, for tests and benchmarks:
  *   0 = automatic (default), 1 = CUDA-core tiled kernel (any shape),
  *   2 = tcgen05 kernel, tokens on the MMA M axis, 3 = tcgen05 kernel, weights on the
