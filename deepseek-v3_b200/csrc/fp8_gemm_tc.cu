@@ -12,8 +12,8 @@
 //
 // Pipeline, in units of K chunks numbered g = 0,1,2,... across all work items of a CTA:
 //   warp 0 (1 lane)  TMA producer : waits empty[g % NS], loads the P and Q tiles of chunk g
-//   warp 1 (1 lane)  MMA issuer   : waits full[g % NS] and tempty[g % NT], issues 4 MMAs,
-//                                   commits to empty[g % NS] and tfull[g % NT]
+//   warps 1,2 (1 lane each) MMA issuers, chunk g belongs to issuer g % 2: wait full[g % NS] and
+//                                   tempty[g % NT], issue 4 MMAs, commit to empty[g % NS] and tfull[g % NT]
 //   warps 4..11      promotion    : wait tfull[g % NT], tcgen05.ld, release tempty, FMA (the load of
 //                                   chunk g+1 is issued before the FMAs of chunk g);
 //                                   at the end of a work item write C (or a split-K partial)
@@ -22,6 +22,12 @@
 //   kSwap = true  : P = 128 rows of b,    Q = BN tokens of a (small M, weights stream once)
 // Split-K: a work item is (tile, split); partial sums go to a workspace and the CTA that
 // takes the last ticket of a tile adds them in split order (deterministic, no spinning).
+//
+// Hand-off costs set the structure: a dependent mbarrier.try_wait takes ~175 cycles even when the
+// phase is already complete and tcgen05.fence::after_thread_sync is of the same order, while a chunk
+// is only ~270 cycles of tensor-core work.  So the issue work is split over two threads, and every
+// role probes the barriers of its next chunk (a non-blocking test_wait whose result is consumed one
+// iteration later) before it starts on the current one.
 //
 // Every wait is bounded: after about a second the waiting thread records what it was
 // waiting for in the status word, raises a CTA-wide abort flag and all roles fall
@@ -38,7 +44,8 @@ namespace dsv3 {
 
 namespace {
 
-constexpr int kNumThreads = 384;          // warp 0: TMA producer, warp 1: MMA issuer, 2-3 idle, 4..11: promotion
+constexpr int kNumThreads = 384;          // warp 0: TMA producer, warps 1-2: MMA issuers, 3 idle, 4..11: promotion
+constexpr int kIssuers = 2;
 constexpr int kPromoThreads = 256;
 constexpr int kFirstPromoWarp = 4;
 
@@ -82,16 +89,20 @@ struct Control {
     volatile int ticket;
 };
 
+// Waits for the phase with the given parity.  The common case costs one or a few try_wait
+// instructions; the wall-clock budget is only consulted after a few thousand failed polls (reading
+// the global timer is slow enough to throttle the pipeline if it sat on the fast path).
 __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, Control* ctl, unsigned int* status,
                                              uint32_t what, uint32_t g) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t t0 = global_timer_ns();
-    uint32_t spins = 0;
-    for (;;) {
+    uint64_t t0 = 0;
+    for (uint32_t spins = 0;; ++spins) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((++spins & 31u) == 0) {
+        if (spins >= 4096u && (spins & 255u) == 0u) {
             if (ctl->abort_flag) return false;
-            if (global_timer_ns() - t0 > kWaitLimitNs) {
+            const uint64_t now = global_timer_ns();
+            if (t0 == 0) {
+                t0 = now;
+            } else if (now - t0 > kWaitLimitNs) {
                 ctl->abort_flag = 1;
                 if (atomicCAS(&status[0], 0u, 1u) == 0u) {
                     status[1] = what;        // 1 empty, 2 full, 3 tmem-empty, 4 tmem-full
@@ -102,6 +113,12 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, Cont
             }
         }
     }
+}
+
+// bounded_wait preceded by the result of an earlier probe of the same barrier and parity.
+__device__ __forceinline__ bool wait_probed(uint32_t probed, uint32_t bar, uint32_t parity, Control* ctl,
+                                            unsigned int* status, uint32_t what, uint32_t g) {
+    return probed != 0u || bounded_wait(bar, parity, ctl, status, what, g);
 }
 
 struct Item {
@@ -194,14 +211,16 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
             uint32_t g = 0;
+            uint32_t probe = 0;   // result of try_wait on empty[] for chunk g, issued one chunk earlier
             bool ok = true;
             for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
                 const Item it = decode_item(item, p);
                 const int p_row = it.p_idx * kPRows, q_row = it.q_idx * BN;
                 for (int ch = it.c0; ch < it.c1; ++ch, ++g) {
                     const int s = g % NS;
-                    ok = bounded_wait(empty_bar(s), ((g / NS) & 1u) ^ 1u, ctl, p.status, 1, g);
+                    ok = wait_probed(probe, empty_bar(s), ((g / NS) & 1u) ^ 1u, ctl, p.status, 1, g);
                     if (!ok) break;
+                    probe = mbar_test_wait(empty_bar((g + 1) % NS), (((g + 1) / NS) & 1u) ^ 1u) ? 1u : 0u;
                     const uint32_t dst = tiles + s * C::kStageBytes;
                     mbar_arrive_expect_tx(full_bar(s), C::kStageBytes);
                     tma_load_2d(dst, &tmap_p, ch * kChunk, p_row, full_bar(s));
@@ -209,19 +228,27 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
                 }
             }
         }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------ MMA issuer
+    } else if (warp <= kIssuers) {
+        // ------------------------------------------------------------ MMA issuers (chunk g -> issuer g % kIssuers)
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc_e4m3_f32(kPRows, BN);
+            const uint32_t me = static_cast<uint32_t>(warp - 1);
             uint32_t g = 0;
+            uint32_t probe_t = 0, probe_f = 0;   // probes of tempty[] / full[] for this issuer's next chunk
             bool ok = true;
             for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
                 const Item it = decode_item(item, p);
                 for (int ch = it.c0; ch < it.c1; ++ch, ++g) {
+                    if (g % kIssuers != me) continue;
                     const int s = g % NS, ts = g % NT;
-                    ok = bounded_wait(tempty_bar(ts), ((g / NT) & 1u) ^ 1u, ctl, p.status, 3, g) &&
-                         bounded_wait(full_bar(s), (g / NS) & 1u, ctl, p.status, 2, g);
+                    ok = wait_probed(probe_t, tempty_bar(ts), ((g / NT) & 1u) ^ 1u, ctl, p.status, 3, g) &&
+                         wait_probed(probe_f, full_bar(s), (g / NS) & 1u, ctl, p.status, 2, g);
                     if (!ok) break;
+                    {   // probe this issuer's next chunk now; the answers are read one iteration later
+                        const uint32_t gn = g + kIssuers;
+                        probe_t = mbar_test_wait(tempty_bar(gn % NT), ((gn / NT) & 1u) ^ 1u) ? 1u : 0u;
+                        probe_f = mbar_test_wait(full_bar(gn % NS), (gn / NS) & 1u) ? 1u : 0u;
+                    }
                     tc_fence_after();
                     const uint32_t sp = tiles + s * C::kStageBytes;
                     const uint64_t dp = umma_desc_k_major_sw128(sp);
@@ -255,11 +282,13 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
         constexpr int SPC = CPT / HC;
         // Issues (does not wait for) the load of step `st` of chunk `gg`; the first step of a chunk
         // first waits for the chunk's product to be complete in TMEM.
+        uint32_t probe = 0;   // result of try_wait on tfull[] for the chunk after the one last waited for
         auto issue_load = [&](uint32_t gg, int st, uint32_t* v) -> bool {
             const int ts = gg % NT;
             if (st == 0) {
-                const bool mine = bounded_wait(tfull_bar(ts), (gg / NT) & 1u, ctl, p.status, 4, gg);
+                const bool mine = wait_probed(probe, tfull_bar(ts), (gg / NT) & 1u, ctl, p.status, 4, gg);
                 if (!__all_sync(0xffffffffu, mine)) return false;
+                probe = mbar_test_wait(tfull_bar((gg + 1) % NT), ((gg + 1) / NT) & 1u) ? 1u : 0u;
                 tc_fence_after();
             }
             tmem_load_cols<HC>(t_lane + ts * BN + st * HC, v);
