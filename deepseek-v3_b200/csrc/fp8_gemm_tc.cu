@@ -14,9 +14,11 @@
 //   warp 0 (1 lane)  TMA producer : waits empty[g % NS], loads the P and Q tiles of chunk g
 //   warps 1,2 (1 lane each) MMA issuers, chunk g belongs to issuer g % 2: wait full[g % NS] and
 //                                   tempty[g % NT], issue 4 MMAs, commit to empty[g % NS] and tfull[g % NT]
-//   warps 4..11      promotion    : wait tfull[g % NT], tcgen05.ld, release tempty, FMA (the load of
-//                                   chunk g+1 is issued before the FMAs of chunk g);
-//                                   at the end of a work item write C (or a split-K partial)
+//   warps 4..7 / 8..11  promotion groups 0 / 1, chunk g belongs to group g % 2: wait tfull[g % NT],
+//                                   tcgen05.ld in 32-column steps (the next step's load is in flight during
+//                                   the FMAs of the current one), release tempty; at the end of a work item
+//                                   group 1 hands its sums to group 0 through shared memory and group 0
+//                                   writes C (or a split-K partial)
 // Operand roles: P is the 128-row MMA "A" operand, Q the BN-row MMA "B" operand.
 //   kSwap = false : P = 128 tokens of a,  Q = 128 rows of b  (large M)
 //   kSwap = true  : P = 128 rows of b,    Q = BN tokens of a (small M, weights stream once)
@@ -35,7 +37,7 @@
 #include <cuda.h>
 
 #include <mutex>
-#include <unordered_map>
+#include <type_traits>
 
 #include "common.cuh"
 #include "gemm_plan.cuh"
@@ -48,6 +50,13 @@ constexpr int kNumThreads = 384;          // warp 0: TMA producer, warps 1-2: MM
 constexpr int kIssuers = 2;
 constexpr int kPromoThreads = 256;
 constexpr int kFirstPromoWarp = 4;
+constexpr int kGroupThreads = 128;        // one promotion group = 4 warps = all 128 TMEM lanes
+constexpr int kTwoGroupMinChunks = 48;    // K chunks per work item from which two promotion groups pay off
+// Register budget: 384 threads start with 168 each; the control warpgroup gives registers back and
+// the two promotion warpgroups take them (up to 128 accumulators + two 32-value load buffers).
+constexpr int kRegsControl = 40;
+constexpr int kRegsPromo = 232;
+static_assert(128 * kRegsControl + 256 * kRegsPromo <= 384 * 168, "register pool");
 
 constexpr int kPRows = 128;               // MMA M
 constexpr int kChunk = 128;               // K elements (= bytes) per chunk
@@ -69,14 +78,16 @@ struct TcParams {
     int num_items;          // tiles_p * tiles_q * splits
 };
 
-template <int BN>
+template <int BN, int G>
 struct Cfg {
     static constexpr int kStageBytes = kPRows * kChunk + BN * kChunk;
-    static constexpr int kStagesRaw = (192 * 1024) / kStageBytes;
+    static constexpr int kExchangeBytes = (G == 2) ? kPRows * BN * 4 : 0;   // one group's accumulators, fp32
+    static constexpr int kStagesRaw = (232448 - 2048 - kExchangeBytes) / kStageBytes;
     static constexpr int kStages = kStagesRaw > 10 ? 10 : kStagesRaw;
     static constexpr int kTmemCols = kTmemStages * BN;  // 64..512, a power of two
-    // tiles + barriers + control words + slack for the 1024-byte alignment of the tiles
-    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 1024;
+    // tiles + exchange buffer + barriers + control words + slack for the 1024-byte alignment of the tiles
+    static constexpr int kSmemBytes = kStages * kStageBytes + kExchangeBytes + 1024 + 1024;
+    static_assert(kSmemBytes <= 232448, "shared memory per CTA");
     static_assert(kTmemCols >= 32 && kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "TMEM columns");
     static_assert((BN * kChunk) % 1024 == 0, "Q tile must keep 1024-byte alignment");
     // more than half of an SM's shared memory, so two CTAs can never share an SM (and its TMEM)
@@ -159,29 +170,38 @@ __device__ __forceinline__ void tmem_load_cols(uint32_t taddr, uint32_t* v) {
     }
 }
 
-__device__ __forceinline__ void promo_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(kPromoThreads) : "memory"); }
+// Barrier among the threads that write results (promotion group 0, or all promotion warps when
+// there is a single group).
+template <int kThreads>
+__device__ __forceinline__ void promo_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory"); }
 
-template <int BN, bool kSwap>
+// G = number of promotion groups: 1 = all eight warps work on every chunk (a thread owns half a row),
+// 2 = two groups of four warps take alternate chunks (a thread owns a whole row) and combine at the end.
+template <int BN, bool kSwap, int G>
 __global__ void __launch_bounds__(kNumThreads, 1)
 fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constant__ CUtensorMap tmap_q,
                    const TcParams p) {
-    using C = Cfg<BN>;
+    using C = Cfg<BN, G>;
     constexpr int NS = C::kStages;
     constexpr int NT = kTmemStages;
-    constexpr int CPT = BN / 2;  // accumulator columns per promotion thread
+    constexpr int CPT = BN * G / 2;   // accumulator columns per promotion thread
+    constexpr int kWriters = (G == 2) ? kGroupThreads : kPromoThreads;   // threads that write results
     static_assert(kSwap || BN == 128, "token-major tiles are 128 x 128 (one b_s value per tile and chunk)");
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t tiles = (raw + 1023u) & ~1023u;
     uint8_t* gen_tiles = smem_raw + (tiles - raw);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(gen_tiles + NS * C::kStageBytes);
-    Control* ctl = reinterpret_cast<Control*>(bars + 2 * NS + 2 * NT);
+    float* exch = reinterpret_cast<float*>(gen_tiles + NS * C::kStageBytes);   // [column][row] fp32
+    uint64_t* bars = reinterpret_cast<uint64_t*>(gen_tiles + NS * C::kStageBytes + C::kExchangeBytes);
+    Control* ctl = reinterpret_cast<Control*>(bars + 2 * NS + 2 * NT + 2);
     const uint32_t bar0 = smem_u32(bars);
     auto full_bar = [&](int s) { return bar0 + 8u * s; };
     auto empty_bar = [&](int s) { return bar0 + 8u * (NS + s); };
     auto tfull_bar = [&](int s) { return bar0 + 8u * (2 * NS + s); };
     auto tempty_bar = [&](int s) { return bar0 + 8u * (2 * NS + NT + s); };
+    const uint32_t exch_full_bar = bar0 + 8u * (2 * NS + 2 * NT);       // group 1 has parked its sums
+    const uint32_t exch_free_bar = bar0 + 8u * (2 * NS + 2 * NT + 1);   // group 0 has read them
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -193,8 +213,10 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
         }
         for (int s = 0; s < NT; ++s) {
             mbar_init(tfull_bar(s), 1);
-            mbar_init(tempty_bar(s), kPromoThreads / 32);
+            mbar_init(tempty_bar(s), kPromoThreads / 32 / G);   // warps that read one stage
         }
+        mbar_init(exch_full_bar, kGroupThreads);
+        mbar_init(exch_free_bar, kGroupThreads);
         ctl->abort_flag = 0;
         ctl->ticket = 0;
         mbar_fence_init();
@@ -206,6 +228,14 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = ctl->tmem_base;
+
+    if constexpr (G == 2) {
+        if (warp < kFirstPromoWarp) {
+            asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsControl));
+        } else {
+            asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsPromo));
+        }
+    }
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
@@ -266,29 +296,35 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
         }
     } else if (warp >= kFirstPromoWarp) {
         // ------------------------------------------------------------ promotion + epilogue
+        // Two groups of four warps; chunk g is promoted by group g % 2, so two chunks are in flight
+        // at any time and each group pays the per-chunk hand-off cost only every other chunk.
+        // A thread owns one accumulator row (TMEM lane) and all BN columns of it.  At the end of a
+        // work item group 1 parks its sums in shared memory, group 0 adds them and writes the result.
+        const int grp = (G == 2) ? (warp - kFirstPromoWarp) >> 2 : 0;
+        const int col0 = (G == 2) ? 0 : ((warp - kFirstPromoWarp) >> 2) * CPT;   // single group: column halves
         const int quarter = warp & 3;                       // TMEM lane quarter this warp may access
-        const int half = (warp - kFirstPromoWarp) >> 2;     // which half of the BN columns
         const int row = quarter * 32 + lane;                // accumulator row (TMEM lane)
-        const int col0 = half * CPT;
         const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + col0;
         const int64_t M = p.M, N = p.N;
         const int kc = p.kc;
-        uint32_t g = 0;
+        uint32_t g = 0;          // chunk counter at the start of the current item (all chunks, both groups)
+        uint32_t item_no = 0;    // items done by this CTA (phase of the exchange barriers)
         bool ok = true;
 
-        // A chunk is read back in SPC steps of HC columns (two steps of 32 for the 64-column case)
-        // so that one step's TMEM load is in flight while the previous step's FMAs issue.
-        constexpr int HC = (CPT == 64) ? 32 : CPT;
+        // A chunk is read back in SPC steps of HC columns so that one step's TMEM load is in flight
+        // while the previous step's FMAs issue.
+        constexpr int HC = (CPT >= 32) ? 32 : CPT;
         constexpr int SPC = CPT / HC;
+        constexpr int U = SPC > 2 ? SPC : 2;   // steps per trip of the pipelined loop (static register indices)
+        uint32_t probe = 0;   // result of test_wait on tfull[] for this group's next chunk
         // Issues (does not wait for) the load of step `st` of chunk `gg`; the first step of a chunk
         // first waits for the chunk's product to be complete in TMEM.
-        uint32_t probe = 0;   // result of try_wait on tfull[] for the chunk after the one last waited for
         auto issue_load = [&](uint32_t gg, int st, uint32_t* v) -> bool {
             const int ts = gg % NT;
             if (st == 0) {
                 const bool mine = wait_probed(probe, tfull_bar(ts), (gg / NT) & 1u, ctl, p.status, 4, gg);
                 if (!__all_sync(0xffffffffu, mine)) return false;
-                probe = mbar_test_wait(tfull_bar((gg + 1) % NT), ((gg + 1) / NT) & 1u) ? 1u : 0u;
+                probe = mbar_test_wait(tfull_bar((gg + G) % NT), ((gg + G) / NT) & 1u) ? 1u : 0u;
                 tc_fence_after();
             }
             tmem_load_cols<HC>(t_lane + ts * BN + st * HC, v);
@@ -305,7 +341,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
             }
         };
 
-        for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
+        for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x, ++item_no) {
             const Item it = decode_item(item, p);
             float2 acc[CPT / 2];
 #pragma unroll
@@ -323,14 +359,22 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
                 as_ptr = p.a_s;
                 bs_ptr = p.b_s + static_cast<int64_t>(it.p_idx) * kc;          // 128 weight rows = one scale row
             }
-            // scale of chunk ch for this thread's row (token-major tiles); index clamped so that the
-            // look-ahead below never leaves the item's chunk range
-            auto row_scale = [&](int ch) -> float {
-                const int c = min(ch, it.c1 - 1);
+            // this group's chunks of the item: local indices first, first + G, ...
+            const int n_ch = it.c1 - it.c0;
+            const int first = (G == 1 || (g & 1u) == static_cast<uint32_t>(grp)) ? 0 : 1;
+            const int n_mine = n_ch > first ? (n_ch - first + G - 1) / G : 0;
+            const int n_steps = n_mine * SPC;
+            auto chunk_g = [&](int mc) -> uint32_t { return g + first + G * mc; };     // pipeline counter
+            auto chunk_k = [&](int mc) -> int { return it.c0 + first + G * mc; };      // K chunk index
+            // scale of this group's mc-th chunk for this thread's row (token-major tiles); clamped so
+            // that the look-ahead never leaves the item
+            auto row_scale = [&](int mc) -> float {
+                const int c = min(chunk_k(mc), it.c1 - 1);
                 return __ldg(as_ptr + c) * __ldg(bs_ptr + c);
             };
-            // acc[off ..] += v * (a_s * b_s) for chunk ch; v holds HC columns starting at column 2*off
-            auto fold = [&](int ch, const uint32_t* v, float sc, int off) {
+            // acc[off ..] += v * (a_s * b_s) for K chunk ch; v holds HC columns starting at column 2*off
+            auto fold = [&](int ch, const uint32_t* v, float sc, auto off_c) {
+                constexpr int off = decltype(off_c)::value;
                 if constexpr (!kSwap) {
                     const float2 sc2 = make_float2(sc, sc);
 #pragma unroll
@@ -341,7 +385,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
                     const float bs = __ldg(bs_ptr + ch);
 #pragma unroll
                     for (int j = 0; j < HC / 2; ++j) {
-                        const int64_t m0 = min(q_base + 2 * j, M - 1), m1 = min(q_base + 2 * j + 1, M - 1);
+                        const int64_t m0 = min(q_base + 2 * (off + j), M - 1), m1 = min(q_base + 2 * (off + j) + 1, M - 1);
                         const float2 sc2 = make_float2(__ldg(as_ptr + m0 * kc + ch) * bs, __ldg(as_ptr + m1 * kc + ch) * bs);
                         acc[off + j] = __ffma2_rn(make_float2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1])),
                                                   sc2, acc[off + j]);
@@ -349,45 +393,71 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
                 }
             };
 
-            // Software pipeline over the load steps of this item, two register buffers.  The loop body
-            // covers two steps: one chunk when SPC == 2, two chunks when SPC == 1.  Row scales
-            // (global memory) are fetched two chunks ahead of their use.
-            const int n_ch = it.c1 - it.c0;
-            const int n_steps = n_ch * SPC;
+            // Software pipeline over the load steps of this group's chunks, two register buffers.  One
+            // trip covers U steps: one chunk when SPC >= 2, two chunks when SPC == 1.  Row scales
+            // (global memory) are fetched two of the group's chunks ahead of their use.
             uint32_t va[HC], vb[HC];
-            float s0 = 0.0f, s1 = 0.0f;
+            float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f;
             if constexpr (!kSwap) {
-                s0 = row_scale(it.c0);
-                s1 = row_scale(it.c0 + 1);
+                s0 = row_scale(0);
+                s1 = row_scale(1);
             }
-            ok = issue_load(g, 0, va);
-            for (int t = 0; ok && t < n_steps; t += 2) {
-                const int ca = t / SPC, cb = (t + 1) / SPC, cc = (t + 2) / SPC;   // chunk of steps t, t+1, t+2
-                float s2 = 0.0f;
-                finish_load(g + ca, t % SPC);
-                if (t + 1 < n_steps) ok = issue_load(g + cb, (t + 1) % SPC, vb);
-                if constexpr (!kSwap) s2 = row_scale(it.c0 + ca + 2);
-                fold(it.c0 + ca, va, s0, 0);
-                if (ok && t + 1 < n_steps) {
-                    finish_load(g + cb, (t + 1) % SPC);
-                    if (t + 2 < n_steps) ok = issue_load(g + cc, (t + 2) % SPC, va);
-                    fold(it.c0 + cb, vb, SPC == 2 ? s0 : s1, SPC == 2 ? HC / 2 : 0);
+            if (n_steps > 0) ok = issue_load(chunk_g(0), 0, va);
+            // step u of the trip starting at step t: finish its load, start the next one, fold
+            auto step = [&](int t, auto u_c, uint32_t* cur, uint32_t* nxt) {
+                constexpr int u = decltype(u_c)::value;
+                constexpr int st = u % SPC;
+                const int T = t + u;
+                if (!ok || T >= n_steps) return;
+                const int mc = T / SPC;
+                finish_load(chunk_g(mc), st);
+                if (T + 1 < n_steps) ok = issue_load(chunk_g((T + 1) / SPC), (u + 1) % SPC, nxt);
+                if constexpr (!kSwap) {
+                    if (st == 0) s2 = row_scale(mc + 2);
                 }
-                if constexpr (SPC == 2) {
+                fold(chunk_k(mc), cur, s0, std::integral_constant<int, st * (HC / 2)>{});
+                if (st == SPC - 1) {   // next chunk of the group
                     s0 = s1;
                     s1 = s2;
-                } else if constexpr (!kSwap) {
-                    s0 = s2;   // unreachable today (token-major tiles always have SPC == 2); kept consistent
-                    s1 = row_scale(it.c0 + ca + 3);
+                }
+            };
+            for (int t = 0; ok && t < n_steps; t += U) {
+                step(t, std::integral_constant<int, 0>{}, va, vb);
+                step(t, std::integral_constant<int, 1>{}, vb, va);
+                if constexpr (U == 4) {
+                    step(t, std::integral_constant<int, 2>{}, va, vb);
+                    step(t, std::integral_constant<int, 3>{}, vb, va);
                 }
             }
             g += n_ch;
             if (!ok) break;
 
-            // ---------------------------------------------------- write-out
+            // ---------------------------------------------------- combine the two groups' sums
+            float* accf = reinterpret_cast<float*>(acc);
+            const uint32_t ex_phase = item_no & 1u;
+            if constexpr (G == 2) {
+              if (grp == 1) {
+                bool mine = bounded_wait(exch_free_bar, ex_phase ^ 1u, ctl, p.status, 5, item_no);
+                ok = __all_sync(0xffffffffu, mine);
+                if (!ok) break;
+#pragma unroll
+                for (int j = 0; j < CPT; ++j) exch[j * kPRows + row] = accf[j];
+                mbar_arrive(exch_full_bar);
+                continue;   // group 0 writes the result
+              }
+              {
+                bool mine = bounded_wait(exch_full_bar, ex_phase, ctl, p.status, 6, item_no);
+                ok = __all_sync(0xffffffffu, mine);
+                if (!ok) break;
+#pragma unroll
+                for (int j = 0; j < CPT; ++j) accf[j] += exch[j * kPRows + row];
+                mbar_arrive(exch_free_bar);
+              }
+            }
+
+            // ---------------------------------------------------- write-out (group 0)
             // normal: thread = token row, CPT consecutive output columns
             // swap  : thread = output column (weight row), CPT tokens
-            const float* accf = reinterpret_cast<const float*>(acc);
             if (p.splits == 1) {
                 if constexpr (!kSwap) {
                     if (p_row < M) {
@@ -445,23 +515,22 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
                     }
                 }
                 __threadfence();
-                promo_barrier();
+                promo_barrier<kWriters>();
                 if (threadIdx.x == kFirstPromoWarp * 32) {
                     const int t = atomicAdd(p.tickets + it.tile, 1);
                     if (t == p.splits - 1) p.tickets[it.tile] = 0;  // last arrival: leave the ticket clean
                     ctl->ticket = t;
                 }
-                promo_barrier();
+                promo_barrier<kWriters>();
                 const bool last = (ctl->ticket == p.splits - 1);
-                promo_barrier();  // everyone has read the ticket before the next item overwrites it
+                promo_barrier<kWriters>();  // everyone has read the ticket before the next item overwrites it
                 if (last) {
                     __threadfence();
                     // sum in split order (deterministic); every trip keeps CPT independent loads in flight
-                    float sum[CPT];
 #pragma unroll
-                    for (int j = 0; j < CPT; ++j) sum[j] = 0.0f;
-                    for (int s = 0; s < p.splits; ++s) {
-                        const float* ps = p.partials + static_cast<int64_t>(s) * M * N;
+                    for (int j = 0; j < CPT; ++j) accf[j] = 0.0f;
+                    for (int sp = 0; sp < p.splits; ++sp) {
+                        const float* ps = p.partials + static_cast<int64_t>(sp) * M * N;
                         if constexpr (!kSwap) {
                             if (p_row < M) {
 #pragma unroll
@@ -469,11 +538,11 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
                                     const int64_t n = q_base + j;
                                     if (vec4 && n + 4 <= N) {
                                         const float4 t4 = __ldcg(reinterpret_cast<const float4*>(ps + p_row * N + n));
-                                        sum[j] += t4.x; sum[j + 1] += t4.y; sum[j + 2] += t4.z; sum[j + 3] += t4.w;
+                                        accf[j] += t4.x; accf[j + 1] += t4.y; accf[j + 2] += t4.z; accf[j + 3] += t4.w;
                                     } else {
 #pragma unroll
                                         for (int e = 0; e < 4; ++e)
-                                            if (n + e < N) sum[j + e] += __ldcg(ps + p_row * N + n + e);
+                                            if (n + e < N) accf[j + e] += __ldcg(ps + p_row * N + n + e);
                                     }
                                 }
                             }
@@ -482,7 +551,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
 #pragma unroll
                                 for (int j = 0; j < CPT; ++j) {
                                     const int64_t m = q_base + j;
-                                    if (m < M) sum[j] += __ldcg(ps + m * N + p_row);
+                                    if (m < M) accf[j] += __ldcg(ps + m * N + p_row);
                                 }
                             }
                         }
@@ -492,7 +561,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
 #pragma unroll
                             for (int j = 0; j < CPT; ++j) {
                                 const int64_t n = q_base + j;
-                                if (n < N) p.c[p_row * N + n] = __float2bfloat16_rn(sum[j]);
+                                if (n < N) p.c[p_row * N + n] = __float2bfloat16_rn(accf[j]);
                             }
                         }
                     } else {
@@ -500,7 +569,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
 #pragma unroll
                             for (int j = 0; j < CPT; ++j) {
                                 const int64_t m = q_base + j;
-                                if (m < M) p.c[m * N + p_row] = __float2bfloat16_rn(sum[j]);
+                                if (m < M) p.c[m * N + p_row] = __float2bfloat16_rn(accf[j]);
                             }
                         }
                     }
@@ -567,10 +636,10 @@ int make_tmap(CUtensorMap* map, const void* base, int64_t rows, int64_t K, int b
     return DSV3_OK;
 }
 
-template <int BN, bool kSwap>
+template <int BN, bool kSwap, int G>
 int launch_variant(const CUtensorMap& tp, const CUtensorMap& tq, const TcParams& prm, cudaStream_t stream) {
-    using C = Cfg<BN>;
-    auto kern = fp8_gemm_tc_kernel<BN, kSwap>;
+    using C = Cfg<BN, G>;
+    auto kern = fp8_gemm_tc_kernel<BN, kSwap, G>;
     static bool configured[64] = {};
     int dev = 0;
     DSV3_CUDA_TRY(cudaGetDevice(&dev));
@@ -667,12 +736,16 @@ int launch_fp8_gemm_tc(const void* a, const float* a_s, const void* b, const flo
     prm.num_items = pl.tiles_p * pl.tiles_q * pl.splits;
     if (pl.swap) {
         switch (pl.bn) {
-            case 16: return launch_variant<16, true>(tp, tq, prm, stream);
-            case 32: return launch_variant<32, true>(tp, tq, prm, stream);
-            case 64: return launch_variant<64, true>(tp, tq, prm, stream);
+            case 16: return launch_variant<16, true, 1>(tp, tq, prm, stream);
+            case 32: return launch_variant<32, true, 1>(tp, tq, prm, stream);
+            case 64: return launch_variant<64, true, 1>(tp, tq, prm, stream);
         }
     } else if (pl.bn == 128) {
-        return launch_variant<128, false>(tp, tq, prm, stream);
+        // long K: two promotion groups on alternate chunks; short K: the end-of-tile combine would
+        // cost more than it saves
+        const int chunks_per_item = pl.kc / pl.splits;
+        if (chunks_per_item >= kTwoGroupMinChunks) return launch_variant<128, false, 2>(tp, tq, prm, stream);
+        return launch_variant<128, false, 1>(tp, tq, prm, stream);
     }
     set_last_error("fp8_gemm: no tcgen05 variant for tile width %d", pl.bn);
     return DSV3_ERR_UNSUPPORTED;
