@@ -78,15 +78,19 @@ struct TcParams {
     int num_items;          // tiles_p * tiles_q * splits
 };
 
-template <int BN, int G>
+constexpr int kScaleTabChunks = 144;      // K chunks of one work item whose scales fit the shared-memory table (K <= 18432)
+
+template <int BN, int G, bool kSwap>
 struct Cfg {
     static constexpr int kStageBytes = kPRows * kChunk + BN * kChunk;
     static constexpr int kExchangeBytes = (G == 2) ? kPRows * BN * 4 : 0;   // one group's accumulators, fp32
-    static constexpr int kStagesRaw = (232448 - 2048 - kExchangeBytes) / kStageBytes;
+    // weight-major tiles: a_s * b_s of the item's chunks for the tile's BN tokens, [chunk][token]
+    static constexpr int kScaleTabBytes = kSwap ? kScaleTabChunks * BN * 4 : 0;
+    static constexpr int kStagesRaw = (232448 - 2048 - kExchangeBytes - kScaleTabBytes) / kStageBytes;
     static constexpr int kStages = kStagesRaw > 10 ? 10 : kStagesRaw;
     static constexpr int kTmemCols = kTmemStages * BN;  // 64..512, a power of two
     // tiles + exchange buffer + barriers + control words + slack for the 1024-byte alignment of the tiles
-    static constexpr int kSmemBytes = kStages * kStageBytes + kExchangeBytes + 1024 + 1024;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kExchangeBytes + kScaleTabBytes + 1024 + 1024;
     static_assert(kSmemBytes <= 232448, "shared memory per CTA");
     static_assert(kTmemCols >= 32 && kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "TMEM columns");
     static_assert((BN * kChunk) % 1024 == 0, "Q tile must keep 1024-byte alignment");
@@ -181,7 +185,7 @@ template <int BN, bool kSwap, int G>
 __global__ void __launch_bounds__(kNumThreads, 1)
 fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constant__ CUtensorMap tmap_q,
                    const TcParams p) {
-    using C = Cfg<BN, G>;
+    using C = Cfg<BN, G, kSwap>;
     constexpr int NS = C::kStages;
     constexpr int NT = kTmemStages;
     constexpr int CPT = BN * G / 2;   // accumulator columns per promotion thread
@@ -193,8 +197,9 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
     const uint32_t tiles = (raw + 1023u) & ~1023u;
     uint8_t* gen_tiles = smem_raw + (tiles - raw);
     float* exch = reinterpret_cast<float*>(gen_tiles + NS * C::kStageBytes);   // [column][row] fp32
-    uint64_t* bars = reinterpret_cast<uint64_t*>(gen_tiles + NS * C::kStageBytes + C::kExchangeBytes);
-    Control* ctl = reinterpret_cast<Control*>(bars + 2 * NS + 2 * NT + 2);
+    float* sc_tab = reinterpret_cast<float*>(gen_tiles + NS * C::kStageBytes + C::kExchangeBytes);   // [chunk][token]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(gen_tiles + NS * C::kStageBytes + C::kExchangeBytes + C::kScaleTabBytes);
+    Control* ctl = reinterpret_cast<Control*>(bars + 2 * NS + 2 * NT + 4);
     const uint32_t bar0 = smem_u32(bars);
     auto full_bar = [&](int s) { return bar0 + 8u * s; };
     auto empty_bar = [&](int s) { return bar0 + 8u * (NS + s); };
@@ -202,6 +207,8 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
     auto tempty_bar = [&](int s) { return bar0 + 8u * (2 * NS + NT + s); };
     const uint32_t exch_full_bar = bar0 + 8u * (2 * NS + 2 * NT);       // group 1 has parked its sums
     const uint32_t exch_free_bar = bar0 + 8u * (2 * NS + 2 * NT + 1);   // group 0 has read them
+    const uint32_t tab_ready_bar = bar0 + 8u * (2 * NS + 2 * NT + 2);   // scale table of the item is filled
+    const uint32_t tab_free_bar = bar0 + 8u * (2 * NS + 2 * NT + 3);    // scale table may be overwritten
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -217,6 +224,8 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
         }
         mbar_init(exch_full_bar, kGroupThreads);
         mbar_init(exch_free_bar, kGroupThreads);
+        mbar_init(tab_ready_bar, kPromoThreads);
+        mbar_init(tab_free_bar, kPromoThreads);
         ctl->abort_flag = 0;
         ctl->ticket = 0;
         mbar_fence_init();
@@ -359,8 +368,29 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
                 as_ptr = p.a_s;
                 bs_ptr = p.b_s + static_cast<int64_t>(it.p_idx) * kc;          // 128 weight rows = one scale row
             }
-            // this group's chunks of the item: local indices first, first + G, ...
             const int n_ch = it.c1 - it.c0;
+            // Weight-major tiles: every thread needs a_s * b_s of all its tokens for every chunk; the
+            // promotion warps put them into shared memory once per item ([chunk][token]) so that the
+            // chunk loop reads them with a few broadcast vector loads.  (The host plan splits K so that an
+            // item never has more chunks than the table holds.)
+            if constexpr (kSwap) {
+                {
+                    bool mine = bounded_wait(tab_free_bar, (item_no & 1u) ^ 1u, ctl, p.status, 7, item_no);
+                    ok = __all_sync(0xffffffffu, mine);
+                    if (!ok) break;
+                    const int tid = threadIdx.x - kFirstPromoWarp * 32;
+                    for (int idx = tid; idx < n_ch * BN; idx += kPromoThreads) {
+                        const int chl = idx / BN, col = idx - chl * BN;
+                        const int64_t m = min(static_cast<int64_t>(it.q_idx) * BN + col, M - 1);
+                        sc_tab[idx] = __ldg(as_ptr + m * kc + it.c0 + chl) * __ldg(bs_ptr + it.c0 + chl);
+                    }
+                    mbar_arrive(tab_ready_bar);
+                    mine = bounded_wait(tab_ready_bar, item_no & 1u, ctl, p.status, 8, item_no);
+                    ok = __all_sync(0xffffffffu, mine);
+                    if (!ok) break;
+                }
+            }
+            // this group's chunks of the item: local indices first, first + G, ...
             const int first = (G == 1 || (g & 1u) == static_cast<uint32_t>(grp)) ? 0 : 1;
             const int n_mine = n_ch > first ? (n_ch - first + G - 1) / G : 0;
             const int n_steps = n_mine * SPC;
@@ -382,14 +412,11 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
                         acc[off + j] = __ffma2_rn(make_float2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1])),
                                                   sc2, acc[off + j]);
                 } else {
-                    const float bs = __ldg(bs_ptr + ch);
+                    const float2* t2 = reinterpret_cast<const float2*>(sc_tab + (ch - it.c0) * BN + col0) + off;
 #pragma unroll
-                    for (int j = 0; j < HC / 2; ++j) {
-                        const int64_t m0 = min(q_base + 2 * (off + j), M - 1), m1 = min(q_base + 2 * (off + j) + 1, M - 1);
-                        const float2 sc2 = make_float2(__ldg(as_ptr + m0 * kc + ch) * bs, __ldg(as_ptr + m1 * kc + ch) * bs);
+                    for (int j = 0; j < HC / 2; ++j)
                         acc[off + j] = __ffma2_rn(make_float2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1])),
-                                                  sc2, acc[off + j]);
-                    }
+                                                  t2[j], acc[off + j]);
                 }
             };
 
@@ -431,6 +458,9 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
             }
             g += n_ch;
             if (!ok) break;
+            if constexpr (kSwap) {
+                mbar_arrive(tab_free_bar);   // this thread is done reading the scale table
+            }
 
             // ---------------------------------------------------- combine the two groups' sums
             float* accf = reinterpret_cast<float*>(acc);
@@ -529,6 +559,9 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
                     // sum in split order (deterministic); every trip keeps CPT independent loads in flight
 #pragma unroll
                     for (int j = 0; j < CPT; ++j) accf[j] = 0.0f;
+                    // (the loop is unrolled so that the loads of four splits are in flight together; the
+                    //  additions still happen in split order)
+#pragma unroll 4
                     for (int sp = 0; sp < p.splits; ++sp) {
                         const float* ps = p.partials + static_cast<int64_t>(sp) * M * N;
                         if constexpr (!kSwap) {
@@ -638,7 +671,7 @@ int make_tmap(CUtensorMap* map, const void* base, int64_t rows, int64_t K, int b
 
 template <int BN, bool kSwap, int G>
 int launch_variant(const CUtensorMap& tp, const CUtensorMap& tq, const TcParams& prm, cudaStream_t stream) {
-    using C = Cfg<BN, G>;
+    using C = Cfg<BN, G, kSwap>;
     auto kern = fp8_gemm_tc_kernel<BN, kSwap, G>;
     static bool configured[64] = {};
     int dev = 0;
@@ -677,18 +710,31 @@ TcPlan tc_plan(int64_t M, int64_t N, int64_t K, int force_kernel, int force_spli
     int splits = 1;
     if (force_split > 0) {
         splits = force_split;
-    } else {
+    } else if (pl.swap) {
+        // Weight-streaming regime: split K until about one wave of work items exists.  Every split
+        // adds a fence + ticket + reduction round to the item's epilogue (several microseconds), so
+        // the factor is kept at or below 8 and rounds down rather than up.
         const int sms = num_sms();
         if (tiles * 2 <= sms) {
-            splits = static_cast<int>((sms + tiles - 1) / tiles);  // enough items for one wave
+            splits = static_cast<int>(sms / tiles);
             const int max_by_k = pl.kc / 2 > 0 ? pl.kc / 2 : 1;     // at least two chunks per split
             if (splits > max_by_k) splits = max_by_k;
-            if (splits > 32) splits = 32;
+            if (splits > 8) splits = 8;
         }
     }
+    // Token-major tiles (M > 64) are never split: measured on B200, the partial-sum round trip costs
+    // more than the idle SMs it would fill (e.g. M=256, N=2048, K=7168: 31 us unsplit, 53 us at 4 splits).
     if (splits > pl.kc) splits = pl.kc;
     if (splits < 1) splits = 1;
     if (tiles > kMaxTickets) splits = 1;
+    if (pl.swap && (pl.kc + splits - 1) / splits > kScaleTabChunks) {
+        // the weight-major kernel keeps an item's scales in a shared-memory table of kScaleTabChunks chunks
+        splits = (pl.kc + kScaleTabChunks - 1) / kScaleTabChunks;
+        if (splits > 32 || tiles > kMaxTickets) {   // absurdly long K: use token-major tiles instead
+            TcPlan alt = tc_plan(M, N, K, 2, 1);
+            return alt;
+        }
+    }
     pl.splits = splits;
     return pl;
 }
