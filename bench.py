@@ -42,8 +42,8 @@ BASE_SHAPES = [
     ("wo", 16384, 7168, "row"),
     ("dense_w13", 7168, 18432, "column"),
     ("dense_w2", 18432, 7168, "row"),
-    ("expert_w13", 7168, 2048, "replicated"),   # routed experts are never TP-sliced
-    ("expert_w2", 2048, 7168, "replicated"),
+    ("expert_w13", 7168, 2048, "expert"),       # routed experts are never TP-sliced: a rank owns whole experts
+    ("expert_w2", 2048, 7168, "expert"),
 ]
 SHARED = [("shared_w13", 7168, 2048, "column"), ("shared_w2", 2048, 7168, "row")]
 
@@ -57,16 +57,42 @@ def shard(shape, tp):
     return shape
 
 
-def sweep_rows(world: int):
-    """Per-rank list of (name, K, N, kind, needs_all_reduce)."""
+def sweep_rows(world: int, rank: int = 0):
+    """Rows of the sweep this rank executes: (name, K, N, kind, needs_all_reduce, counted).
+
+    The global problem set is the same for every world size (BASELINE configs[1]: the 9 full Linear shapes
+    and 7 shapes that are already the TP=8 per-rank slice).  With more than one rank it is spread the way the
+    reference's tensor parallelism spreads it (model.py:208-267, 636-666):
+      * column-parallel: every rank N/ws rows of W; row-parallel: every rank K/ws columns of W, partial
+        outputs summed with all_reduce;
+      * replicated Linears (wq_a, wkv_a) run on every rank, as they do in the model; their flops are
+        counted once;
+      * whole-expert GEMMs and the ready-made TP=8 slices are single-rank problems: each is owned by one
+        rank (round-robin), the way different ranks own different experts.
+    `counted` says whether this rank's execution adds to the job's flop count."""
+    slices = [shard(s, 8) for s in BASE_SHAPES + SHARED if s[3] in ("column", "row")]
+    slices = [(n.replace("/tp8", "@tp8-slice"), k, o, kind) for n, k, o, kind in slices]
     if world == 1:
-        rows = [(n, k, o, kind, False) for n, k, o, kind in BASE_SHAPES]
-        rows += [(*shard(s, 8), False) for s in BASE_SHAPES + SHARED if s[3] != "replicated"]
+        rows = [(n, k, o, kind, False, True) for n, k, o, kind in BASE_SHAPES]
+        rows += [(n, k, o, kind, False, True) for n, k, o, kind in slices]
         return rows
     rows = []
-    for s in BASE_SHAPES + SHARED:
-        n, k, o, kind = shard(s, world)
-        rows.append((n, k, o, kind, kind == "row"))
+    owner = 0
+    for s in BASE_SHAPES:
+        n, k, o, kind = s
+        if kind in ("column", "row"):
+            n, k, o, kind = shard(s, world)
+            rows.append((n, k, o, kind, kind == "row", True))
+        elif kind == "replicated":
+            rows.append((n, k, o, kind, False, rank == 0))
+        else:  # expert
+            if owner % world == rank:
+                rows.append((n, k, o, kind, False, True))
+            owner += 1
+    for n, k, o, kind in slices:
+        if owner % world == rank:
+            rows.append((n, k, o, "slice", False, True))
+        owner += 1
     return rows
 
 
@@ -143,7 +169,7 @@ def cpu_sample_inputs(rows, M, seed=0):
     from oracle import oracle as O
     g = torch.Generator().manual_seed(seed)
     cases = []
-    for name, K, N, _, _ in rows:
+    for name, K, N, *_ in rows:
         w = (torch.randn(N, K, generator=g) * 0.02).to(torch.bfloat16)
         wq, ws = O.weight_quant(w)
         x = torch.randn(M, K, generator=g).to(torch.bfloat16)
@@ -195,14 +221,16 @@ def run_reference(args):
 
 
 def workload_config(world):
-    rows = sweep_rows(world)
+    rows = sweep_rows(1)
     return {
         "workload": "BASELINE configs[1]: fp8_gemm sweep over DeepSeek-V3 Linear shapes (dim 7168), "
                     f"{len(rows)} (K->N) rows x M in {MS}; activations N(0,1) bf16 -> act_quant, weights N(0,0.02) "
                     "quantised per 128x128 block",
-        "shapes": [f"{n}:{k}->{o}" for n, k, o, _, _ in rows],
+        "shapes": [f"{n}:{k}->{o}" for n, k, o, *_ in rows],
         "m_values": MS, "block_size": 128,
-        "parallelism": "single GPU" if world == 1 else f"tp{world}: column N/ws, row K/ws + NCCL all_reduce",
+        "parallelism": "single GPU" if world == 1 else
+                       f"tp{world}: the same problem set; column-parallel N/ws, row-parallel K/ws + NCCL all_reduce, "
+                       "replicated Linears on every rank (counted once), expert and TP=8-slice problems owned round-robin",
         "l2": "inputs larger than L2: the sweep runs M-major, so >500 MB of other weights stream between two "
               "uses of any weight (L2 is 126 MB)",
     }
@@ -230,7 +258,7 @@ def run_ours(args):
     torch.set_default_dtype(torch.bfloat16)
     torch.manual_seed(1234 + rank)
     peaks = read_peaks()
-    rows = sweep_rows(world)
+    rows = sweep_rows(world, rank)
 
     # ---- synthetic, resident inputs -------------------------------------------------
     Mmax = max(MS)
@@ -240,16 +268,23 @@ def run_ours(args):
         xq, xs = kernel.act_quant(x)
         acts[K] = (x, xq, xs)
     weights = {}
-    for name, K, N, _, _ in rows:
+    for name, K, N, *_ in rows:
         w = (torch.randn(N, K, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
         weights[name] = dsv3_b200.weight_quant(w)
         del w
-    plan = [(name, K, N, M, ar) for M in MS for (name, K, N, _, ar) in rows]   # M-major
-    total_flops = sum(gemm_flops(M, N, K) for _, K, N, M, _ in plan)
+    plan = [(name, K, N, M, ar) for M in MS for (name, K, N, _, ar, _c) in rows]   # M-major
+    my_flops = sum(gemm_flops(M, N, K) for M in MS for (_, K, N, _, _, counted) in rows if counted)
+    total_flops = my_flops
+    if world > 1:
+        tt = torch.tensor([my_flops], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt)
+        total_flops = tt.item()
+    ref_flops = sum(gemm_flops(M, N, K) for M in MS for (_, K, N, *_r) in sweep_rows(1))
+    assert abs(total_flops - ref_flops) <= 1e-9 * ref_flops, (total_flops, ref_flops)
 
     def column(M):
         """fp8_gemm for every shape of the sweep at one M (one CUDA graph per column)."""
-        for name, K, N, _, ar in rows:
+        for name, K, N, _, ar, _c in rows:
             _, xq, xs = acts[K]
             wq, ws = weights[name]
             y = kernel.fp8_gemm(xq[:M], xs[:M], wq, ws)
@@ -346,8 +381,8 @@ def run_ours(args):
     for marks in col_events:
         for i, M in enumerate(MS):
             dt = marks[i].elapsed_time(marks[i + 1]) * 1e-3
-            fl = sum(gemm_flops(M, N, K) for _, K, N, _, _ in rows)
-            by = sum(gemm_bytes(M, N, K) for _, K, N, _, _ in rows)
+            fl = sum(gemm_flops(M, N, K) for _, K, N, *_r in rows)
+            by = sum(gemm_bytes(M, N, K) for _, K, N, *_r in rows)
             acc = per_column.setdefault(M, [0.0, 0, fl, by])
             acc[0] += dt; acc[1] += 1
             if M >= 256:
@@ -373,11 +408,22 @@ def run_ours(args):
     detail = {f"M={k}": {"us_per_column": v[0] / v[1] * 1e6, "tflops": v[2] / (v[0] / v[1]) / 1e12,
                          "gbs": v[3] / (v[0] / v[1]) / 1e9, "launches": len(rows)} for k, v in per_column.items()}
 
-    if world > 1:
+    def shutdown():
+        """Tear down in an order NCCL accepts: graphs that captured collectives go first.  A timer ends
+        the process if the teardown itself blocks (the measurement is already printed by then)."""
+        if world == 1:
+            return
+        killer = threading.Timer(45.0, lambda: os._exit(0))
+        killer.daemon = True
+        killer.start()
+        graphs.clear()
+        torch.cuda.synchronize()
         dist.barrier()
+        dist.destroy_process_group()
+        killer.cancel()
+
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
+        shutdown()
         return
 
     # ---- CPU baseline (rank 0, N=1 only): the oracle on a bounded sample ----------------
@@ -389,8 +435,8 @@ def run_ours(args):
         cpu = {"value": fl / dt / 1e12, "unit": "TFLOP/s", "cores": O.num_threads(), "kind": "port",
                "sample": f"M=64 column of the sweep ({len(cases)} shapes), act_quant+fp8_gemm per shape, one pass, {dt:.1f} s"}
 
-    agg = total_flops * world * args.steps / (ms * 1e-3) / 1e12
-    agg_e2e = total_flops * world * args.steps / (ms_e2e * 1e-3) / 1e12
+    agg = total_flops * args.steps / (ms * 1e-3) / 1e12
+    agg_e2e = total_flops * args.steps / (ms_e2e * 1e-3) / 1e12
     line = {
         "metric": "fp8_gemm_tflops_v3_shape_sweep", "value": agg, "unit": "TFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
@@ -405,8 +451,7 @@ def run_ours(args):
         "clocks": clocks, "per_column": detail,
     }
     print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    shutdown()
 
 
 def run_single(args):
@@ -461,7 +506,7 @@ def run_detail(args):
     ms_list = [int(v) for v in args.detail_m.split(",")] if args.detail_m else MS
     side = torch.cuda.Stream(device=dev)
     out = []
-    for name, K, N, _, _ in rows:
+    for name, K, N, *_ in rows:
         R = max(2, min(64, -(-(256 << 20) // (N * K))))
         w = (torch.randn(N, K, device=dev, dtype=torch.float32) * 0.02).to(torch.bfloat16)
         wq0, ws0 = dsv3_b200.weight_quant(w)
