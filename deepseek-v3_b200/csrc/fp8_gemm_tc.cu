@@ -711,15 +711,20 @@ TcPlan tc_plan(int64_t M, int64_t N, int64_t K, int force_kernel, int force_spli
     if (force_split > 0) {
         splits = force_split;
     } else if (pl.swap) {
-        // Weight-streaming regime: split K until about one wave of work items exists.  Every split
-        // adds a fence + ticket + reduction round to the item's epilogue (several microseconds), so
-        // the factor is kept at or below 8 and rounds down rather than up.
+        // Weight-streaming regime.  Splitting K fills idle SMs but every split item pays a fence + ticket
+        // + reduction round in its epilogue.  Cost model fitted to B200 measurements (microseconds):
+        //   rounds(S) * chunks_per_item(S) * 0.42  +  (S > 1 ? 4.0 : 0)
+        // with rounds = ceil(tiles * S / SMs); the factor with the lowest estimate wins (ties: fewer splits).
         const int sms = num_sms();
-        if (tiles * 2 <= sms) {
-            splits = static_cast<int>(sms / tiles);
-            const int max_by_k = pl.kc / 2 > 0 ? pl.kc / 2 : 1;     // at least two chunks per split
-            if (splits > max_by_k) splits = max_by_k;
-            if (splits > 8) splits = 8;
+        double best = 1e30;
+        for (int sfac = 1; sfac <= 8 && sfac <= pl.kc; ++sfac) {
+            const int64_t rounds = (tiles * sfac + sms - 1) / sms;
+            const int per_item = (pl.kc + sfac - 1) / sfac;
+            const double t = static_cast<double>(rounds) * per_item * 0.42 + (sfac > 1 ? 4.0 : 0.0);
+            if (t < best - 1e-9) {
+                best = t;
+                splits = sfac;
+            }
         }
     }
     // Token-major tiles (M > 64) are never split: measured on B200, the partial-sum round trip costs

@@ -24,23 +24,47 @@ __device__ __forceinline__ uint4 dequant8(uint32_t lo, uint32_t hi, float s) {
                       pack_bf16x2(__fmul_rn(c.x, s), __fmul_rn(c.y, s)), pack_bf16x2(__fmul_rn(d.x, s), __fmul_rn(d.y, s)));
 }
 
-// K % 16 == 0: a 16-element group never straddles a scale block (block % 16 == 0).
-// Index is uint32_t when the group count fits (64-bit division per group would make the
-// kernel instruction-bound), int64_t otherwise.
-template <typename Index>
-__global__ void __launch_bounds__(kThreads) weight_dequant_vec_kernel(const uint4* __restrict__ w,
+// Division of a 32-bit index by a run-time constant: n / d == (umulhi(n, magic) + n) >> shift
+// (round-up method; the intermediate sum needs 33 bits, hence the 64-bit add).
+struct FastDiv {
+    uint32_t magic, shift, d;
+};
+__device__ __forceinline__ uint32_t fast_div(uint32_t n, const FastDiv& f) {
+    return static_cast<uint32_t>((static_cast<uint64_t>(__umulhi(n, f.magic)) + n) >> f.shift);
+}
+
+constexpr int kVecUnroll = 8;   // independent 16-byte loads in flight per thread
+
+// K % 16 == 0 and a power-of-two block size: a 16-element group never straddles a scale block.
+// A thread converts kVecUnroll groups per trip, all loads issued before the first use, so that
+// 64 bytes per thread (128 KB per SM at full occupancy) are in flight.
+__global__ void __launch_bounds__(kThreads, 4) weight_dequant_vec_kernel(const uint4* __restrict__ w,
                                                                        const float* __restrict__ s,
-                                                                       uint4* __restrict__ y, Index total,
-                                                                       Index groups_per_row, Index block,
-                                                                       Index kb) {
-    const Index stride = static_cast<Index>(gridDim.x) * kThreads;
-    for (Index g = static_cast<Index>(blockIdx.x) * kThreads + threadIdx.x; g < total; g += stride) {
-        const Index n = g / groups_per_row;
-        const Index k = (g - n * groups_per_row) << 4;
-        const float sc = __ldg(s + static_cast<size_t>(n / block) * kb + (k / block));
-        const uint4 v = __ldcs(w + g);
-        __stcs(y + 2 * static_cast<size_t>(g), dequant8(v.x, v.y, sc));
-        __stcs(y + 2 * static_cast<size_t>(g) + 1, dequant8(v.z, v.w, sc));
+                                                                       uint4* __restrict__ y, uint32_t total,
+                                                                       FastDiv row_div, uint32_t block_shift,
+                                                                       uint32_t kb) {
+    const uint32_t stride = gridDim.x * kThreads;
+    for (uint32_t g0 = blockIdx.x * kThreads + threadIdx.x; g0 < total; g0 += stride * kVecUnroll) {
+        uint4 v[kVecUnroll];
+        float sc[kVecUnroll];
+#pragma unroll
+        for (int u = 0; u < kVecUnroll; ++u) {
+            const uint32_t g = g0 + u * stride;
+            if (g < total) {
+                v[u] = __ldg(w + g);
+                const uint32_t n = fast_div(g, row_div);
+                const uint32_t k = (g - n * row_div.d) << 4;
+                sc[u] = __ldg(s + static_cast<size_t>(n >> block_shift) * kb + (k >> block_shift));
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kVecUnroll; ++u) {
+            const uint32_t g = g0 + u * stride;
+            if (g < total) {
+                y[2 * static_cast<size_t>(g)] = dequant8(v[u].x, v[u].y, sc[u]);
+                y[2 * static_cast<size_t>(g) + 1] = dequant8(v[u].z, v[u].w, sc[u]);
+            }
+        }
     }
 }
 
@@ -94,20 +118,25 @@ int launch_weight_dequant(const void* w, const float* s, int64_t N, int64_t K, i
     if (N == 0 || K == 0) return DSV3_OK;
     const int64_t kb = (K + block - 1) / block;
     const int64_t cap = static_cast<int64_t>(num_sms()) * 8;
-    const bool vec = (K % 16 == 0) && (block % 16 == 0) && (reinterpret_cast<uintptr_t>(w) % 16 == 0) &&
-                     (reinterpret_cast<uintptr_t>(y) % 16 == 0);
+    const bool pow2 = (block & (block - 1)) == 0;
+    const int64_t total = N * (K >> 4);
+    const bool vec = (K % 16 == 0) && pow2 && block >= 16 && (reinterpret_cast<uintptr_t>(w) % 16 == 0) &&
+                     (reinterpret_cast<uintptr_t>(y) % 16 == 0) && total < (1ll << 31) && kb < (1ll << 31);
     if (vec) {
-        const int64_t total = N * (K >> 4);
-        int64_t grid = (total + kThreads - 1) / kThreads;
+        const int64_t per_cta = static_cast<int64_t>(kThreads) * kVecUnroll;
+        int64_t grid = (total + per_cta - 1) / per_cta;
         if (grid > cap) grid = cap;
-        if (total < (1ll << 31) && kb < (1ll << 31)) {
-            weight_dequant_vec_kernel<uint32_t><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
-                static_cast<const uint4*>(w), s, static_cast<uint4*>(y), static_cast<uint32_t>(total),
-                static_cast<uint32_t>(K >> 4), static_cast<uint32_t>(block), static_cast<uint32_t>(kb));
-        } else {
-            weight_dequant_vec_kernel<int64_t><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
-                static_cast<const uint4*>(w), s, static_cast<uint4*>(y), total, K >> 4, static_cast<int64_t>(block), kb);
-        }
+        FastDiv fd;
+        fd.d = static_cast<uint32_t>(K >> 4);
+        uint32_t sh = 0;
+        while ((1ull << sh) < fd.d) ++sh;
+        fd.shift = sh;
+        fd.magic = static_cast<uint32_t>(((1ull << 32) * ((1ull << sh) - fd.d)) / fd.d + 1);
+        uint32_t bshift = 0;
+        while ((1 << bshift) < block) ++bshift;
+        weight_dequant_vec_kernel<<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
+            static_cast<const uint4*>(w), s, static_cast<uint4*>(y), static_cast<uint32_t>(total), fd, bshift,
+            static_cast<uint32_t>(kb));
     } else {
         int64_t grid = (N * K + kThreads - 1) / kThreads;
         if (grid > cap) grid = cap;
