@@ -36,8 +36,10 @@
 // through to the common teardown (which frees TMEM).
 #include <cuda.h>
 
+#include <cstring>
 #include <mutex>
 #include <type_traits>
+#include <vector>
 
 #include "common.cuh"
 #include "gemm_plan.cuh"
@@ -76,6 +78,13 @@ struct TcParams {
     int tiles_p, tiles_q;
     int splits;
     int num_items;          // tiles_p * tiles_q * splits
+    // Grouped mode (MoE experts; weight-major tiles only, no split-K): group e multiplies the activation
+    // rows [g_seg[e], g_seg[e+1]) with its own weight.  n_groups == 0 means one ordinary GEMM.
+    const CUtensorMap* g_tmaps;    // per-group weight tensor maps, in global memory
+    const float* const* g_bs;      // per-group weight scale pointers, in global memory
+    const int* g_seg;              // [n_groups + 1] row offsets, in global memory (written on the device)
+    int n_groups;
+    int g_slots;                   // upper bound on the number of token tiles over all groups
 };
 
 constexpr int kScaleTabChunks = 144;      // K chunks of one work item whose scales fit the shared-memory table (K <= 18432)
@@ -86,11 +95,12 @@ struct Cfg {
     static constexpr int kExchangeBytes = (G == 2) ? kPRows * BN * 4 : 0;   // one group's accumulators, fp32
     // weight-major tiles: a_s * b_s of the item's chunks for the tile's BN tokens, [chunk][token]
     static constexpr int kScaleTabBytes = kSwap ? kScaleTabChunks * BN * 4 : 0;
-    static constexpr int kStagesRaw = (232448 - 2048 - kExchangeBytes - kScaleTabBytes) / kStageBytes;
+    static constexpr int kGroupTabBytes = kSwap ? 2048 : 0;   // grouped mode: token-tile prefix per group
+    static constexpr int kStagesRaw = (232448 - 2048 - kExchangeBytes - kScaleTabBytes - kGroupTabBytes) / kStageBytes;
     static constexpr int kStages = kStagesRaw > 10 ? 10 : kStagesRaw;
     static constexpr int kTmemCols = kTmemStages * BN;  // 64..512, a power of two
     // tiles + exchange buffer + barriers + control words + slack for the 1024-byte alignment of the tiles
-    static constexpr int kSmemBytes = kStages * kStageBytes + kExchangeBytes + kScaleTabBytes + 1024 + 1024;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kExchangeBytes + kScaleTabBytes + kGroupTabBytes + 1024 + 1024;
     static_assert(kSmemBytes <= 232448, "shared memory per CTA");
     static_assert(kTmemCols >= 32 && kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "TMEM columns");
     static_assert((BN * kChunk) % 1024 == 0, "Q tile must keep 1024-byte alignment");
@@ -138,11 +148,44 @@ __device__ __forceinline__ bool wait_probed(uint32_t probed, uint32_t bar, uint3
 
 struct Item {
     int p_idx, q_idx, split, tile;
-    int c0, c1;  // chunk range
+    int c0, c1;     // chunk range
+    int group;      // grouped mode: which weight
+    int row0;       // weight-major tiles: first activation row of the tile
+    int row_end;    // weight-major tiles: activation rows at and beyond this index are not part of the problem
 };
 
-__device__ __forceinline__ Item decode_item(int item, const TcParams& p) {
+constexpr int kMaxGroups = 256;
+
+// g_prefix (shared memory, grouped mode): g_prefix[e] = number of token tiles of the groups before e.
+template <int BN, bool kSwap>
+__device__ __forceinline__ Item decode_item(int item, const TcParams& p, const int* g_prefix) {
     Item it;
+    if (kSwap && p.n_groups > 0) {
+        // item -> (weight tile p_idx, token-tile slot); slot -> (group, tile within the group) by binary search
+        it.p_idx = item % p.tiles_p;
+        const int slot = item / p.tiles_p;
+        it.tile = item;
+        it.split = 0;
+        it.q_idx = 0;
+        int lo = 0, hi = p.n_groups;          // invariant: g_prefix[lo] <= slot, answer in [lo, hi)
+        if (slot >= g_prefix[p.n_groups]) {   // beyond the last real tile: an empty item
+            it.group = 0;
+            it.row0 = it.row_end = 0;
+            it.c0 = it.c1 = 0;
+            return it;
+        }
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (g_prefix[mid] <= slot) lo = mid; else hi = mid;
+        }
+        it.group = lo;
+        it.row0 = __ldg(p.g_seg + lo) + (slot - g_prefix[lo]) * BN;
+        it.row_end = __ldg(p.g_seg + lo + 1);
+        it.c0 = 0;
+        it.c1 = p.kc;
+        return it;
+    }
+    it.group = 0;
     it.tile = item / p.splits;
     it.split = item - it.tile * p.splits;
     // grouped raster: 8 P-tiles share consecutive Q-tiles so a wave re-uses both operands in L2
@@ -156,6 +199,8 @@ __device__ __forceinline__ Item decode_item(int item, const TcParams& p) {
     it.q_idx = r / gsz;
     it.c0 = static_cast<int>((static_cast<int64_t>(p.kc) * it.split) / p.splits);
     it.c1 = static_cast<int>((static_cast<int64_t>(p.kc) * (it.split + 1)) / p.splits);
+    it.row0 = it.q_idx * BN;
+    it.row_end = static_cast<int>(p.M);
     return it;
 }
 
@@ -198,7 +243,9 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
     uint8_t* gen_tiles = smem_raw + (tiles - raw);
     float* exch = reinterpret_cast<float*>(gen_tiles + NS * C::kStageBytes);   // [column][row] fp32
     float* sc_tab = reinterpret_cast<float*>(gen_tiles + NS * C::kStageBytes + C::kExchangeBytes);   // [chunk][token]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(gen_tiles + NS * C::kStageBytes + C::kExchangeBytes + C::kScaleTabBytes);
+    int* g_prefix = reinterpret_cast<int*>(gen_tiles + NS * C::kStageBytes + C::kExchangeBytes + C::kScaleTabBytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(gen_tiles + NS * C::kStageBytes + C::kExchangeBytes + C::kScaleTabBytes +
+                                                 C::kGroupTabBytes);
     Control* ctl = reinterpret_cast<Control*>(bars + 2 * NS + 2 * NT + 4);
     const uint32_t bar0 = smem_u32(bars);
     auto full_bar = [&](int s) { return bar0 + 8u * s; };
@@ -233,6 +280,24 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
         tma_prefetch_desc(&tmap_q);
     }
     if (warp == 1) tc_alloc(smem_u32(&ctl->tmem_base), C::kTmemCols);
+    if constexpr (kSwap) {
+        if (p.n_groups > 0) {
+            // token tiles per group, then an exclusive prefix sum (n_groups <= kMaxGroups)
+            for (int e = threadIdx.x; e < p.n_groups; e += kNumThreads) {
+                const int cnt = __ldg(p.g_seg + e + 1) - __ldg(p.g_seg + e);
+                g_prefix[e + 1] = (cnt + BN - 1) / BN;
+            }
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                int run = 0;
+                g_prefix[0] = 0;
+                for (int e = 1; e <= p.n_groups; ++e) {
+                    run += g_prefix[e];
+                    g_prefix[e] = run;
+                }
+            }
+        }
+    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -253,8 +318,11 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
             uint32_t probe = 0;   // result of try_wait on empty[] for chunk g, issued one chunk earlier
             bool ok = true;
             for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
-                const Item it = decode_item(item, p);
-                const int p_row = it.p_idx * kPRows, q_row = it.q_idx * BN;
+                const Item it = decode_item<BN, kSwap>(item, p, g_prefix);
+                const int p_row = it.p_idx * kPRows;
+                const int q_row = kSwap ? it.row0 : it.q_idx * BN;
+                const void* map_p = (kSwap && p.n_groups > 0) ? static_cast<const void*>(p.g_tmaps + it.group)
+                                                               : static_cast<const void*>(&tmap_p);
                 for (int ch = it.c0; ch < it.c1; ++ch, ++g) {
                     const int s = g % NS;
                     ok = wait_probed(probe, empty_bar(s), ((g / NS) & 1u) ^ 1u, ctl, p.status, 1, g);
@@ -262,7 +330,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
                     probe = mbar_test_wait(empty_bar((g + 1) % NS), (((g + 1) / NS) & 1u) ^ 1u) ? 1u : 0u;
                     const uint32_t dst = tiles + s * C::kStageBytes;
                     mbar_arrive_expect_tx(full_bar(s), C::kStageBytes);
-                    tma_load_2d(dst, &tmap_p, ch * kChunk, p_row, full_bar(s));
+                    tma_load_2d(dst, map_p, ch * kChunk, p_row, full_bar(s));
                     tma_load_2d(dst + kPRows * kChunk, &tmap_q, ch * kChunk, q_row, full_bar(s));
                 }
             }
@@ -276,7 +344,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
             uint32_t probe_t = 0, probe_f = 0;   // probes of tempty[] / full[] for this issuer's next chunk
             bool ok = true;
             for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
-                const Item it = decode_item(item, p);
+                const Item it = decode_item<BN, kSwap>(item, p, g_prefix);
                 for (int ch = it.c0; ch < it.c1; ++ch, ++g) {
                     if (g % kIssuers != me) continue;
                     const int s = g % NS, ts = g % NT;
@@ -351,14 +419,15 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
         };
 
         for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x, ++item_no) {
-            const Item it = decode_item(item, p);
+            const Item it = decode_item<BN, kSwap>(item, p, g_prefix);
             float2 acc[CPT / 2];
 #pragma unroll
             for (int j = 0; j < CPT / 2; ++j) acc[j] = make_float2(0.0f, 0.0f);
 
             // token / weight-row coordinates of this thread
             const int64_t p_row = static_cast<int64_t>(it.p_idx) * kPRows + row;
-            const int64_t q_base = static_cast<int64_t>(it.q_idx) * BN + col0;
+            const int64_t q_base = (kSwap ? static_cast<int64_t>(it.row0) : static_cast<int64_t>(it.q_idx) * BN) + col0;
+            const int64_t m_end = kSwap ? static_cast<int64_t>(it.row_end) : M;   // weight-major: token rows of this item end here
             const float* as_ptr;  // normal: this row's scales ; swap: scale matrix, indexed per token below
             const float* bs_ptr;
             if constexpr (!kSwap) {
@@ -366,7 +435,8 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
                 bs_ptr = p.b_s + static_cast<int64_t>(it.q_idx) * kc;          // BN == 128
             } else {
                 as_ptr = p.a_s;
-                bs_ptr = p.b_s + static_cast<int64_t>(it.p_idx) * kc;          // 128 weight rows = one scale row
+                const float* bs_base = (p.n_groups > 0) ? p.g_bs[it.group] : p.b_s;
+                bs_ptr = bs_base + static_cast<int64_t>(it.p_idx) * kc;        // 128 weight rows = one scale row
             }
             const int n_ch = it.c1 - it.c0;
             // Weight-major tiles: every thread needs a_s * b_s of all its tokens for every chunk; the
@@ -381,7 +451,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
                     const int tid = threadIdx.x - kFirstPromoWarp * 32;
                     for (int idx = tid; idx < n_ch * BN; idx += kPromoThreads) {
                         const int chl = idx / BN, col = idx - chl * BN;
-                        const int64_t m = min(static_cast<int64_t>(it.q_idx) * BN + col, M - 1);
+                        const int64_t m = max(min(static_cast<int64_t>(it.row0) + col, m_end - 1), static_cast<int64_t>(0));
                         sc_tab[idx] = __ldg(as_ptr + m * kc + it.c0 + chl) * __ldg(bs_ptr + it.c0 + chl);
                     }
                     mbar_arrive(tab_ready_bar);
@@ -512,7 +582,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
 #pragma unroll
                         for (int j = 0; j < CPT; ++j) {
                             const int64_t m = q_base + j;
-                            if (m < M) p.c[m * N + p_row] = __float2bfloat16_rn(accf[j]);
+                            if (m < m_end) p.c[m * N + p_row] = __float2bfloat16_rn(accf[j]);
                         }
                     }
                 }
@@ -540,7 +610,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
 #pragma unroll
                         for (int j = 0; j < CPT; ++j) {
                             const int64_t m = q_base + j;
-                            if (m < M) __stcg(part + m * N + p_row, accf[j]);
+                            if (m < m_end) __stcg(part + m * N + p_row, accf[j]);
                         }
                     }
                 }
@@ -584,7 +654,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
 #pragma unroll
                                 for (int j = 0; j < CPT; ++j) {
                                     const int64_t m = q_base + j;
-                                    if (m < M) accf[j] += __ldcg(ps + m * N + p_row);
+                                    if (m < m_end) accf[j] += __ldcg(ps + m * N + p_row);
                                 }
                             }
                         }
@@ -602,7 +672,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
 #pragma unroll
                             for (int j = 0; j < CPT; ++j) {
                                 const int64_t m = q_base + j;
-                                if (m < M) p.c[m * N + p_row] = __float2bfloat16_rn(accf[j]);
+                                if (m < m_end) p.c[m * N + p_row] = __float2bfloat16_rn(accf[j]);
                             }
                         }
                     }
@@ -785,6 +855,11 @@ int launch_fp8_gemm_tc(const void* a, const float* a_s, const void* b, const flo
     prm.tiles_q = pl.tiles_q;
     prm.splits = pl.splits;
     prm.num_items = pl.tiles_p * pl.tiles_q * pl.splits;
+    prm.g_tmaps = nullptr;
+    prm.g_bs = nullptr;
+    prm.g_seg = nullptr;
+    prm.n_groups = 0;
+    prm.g_slots = 0;
     if (pl.swap) {
         switch (pl.bn) {
             case 16: return launch_variant<16, true, 1>(tp, tq, prm, stream);
@@ -800,6 +875,94 @@ int launch_fp8_gemm_tc(const void* a, const float* a_s, const void* b, const flo
     }
     set_last_error("fp8_gemm: no tcgen05 variant for tile width %d", pl.bn);
     return DSV3_ERR_UNSUPPORTED;
+}
+
+
+// ---------------------------------------------------------------------------------------------
+// Grouped GEMM (MoE experts): one launch, group e multiplies rows [seg[e], seg[e+1]) of `a` with its
+// own weight.  The table holds, in device memory, n tensor maps followed by n scale pointers.
+// ---------------------------------------------------------------------------------------------
+size_t group_table_bytes(int n) { return static_cast<size_t>(n) * (sizeof(CUtensorMap) + sizeof(const float*)); }
+
+int build_group_table(void* table_dev, const void* const* weights, const float* const* scales, int n, int64_t N,
+                      int64_t K, cudaStream_t stream) {
+    if (n <= 0 || n > kMaxGroups) {
+        set_last_error("group table: between 1 and %d groups are supported (got %d)", kMaxGroups, n);
+        return DSV3_ERR_UNSUPPORTED;
+    }
+    if ((K % 16) != 0 || (reinterpret_cast<uintptr_t>(table_dev) % 64) != 0) {
+        set_last_error("group table: needs K %% 16 == 0 and a 64-byte aligned table");
+        return DSV3_ERR_UNSUPPORTED;
+    }
+    std::vector<uint8_t> host(group_table_bytes(n));
+    CUtensorMap* maps = reinterpret_cast<CUtensorMap*>(host.data());
+    const float** sp = reinterpret_cast<const float**>(host.data() + static_cast<size_t>(n) * sizeof(CUtensorMap));
+    for (int e = 0; e < n; ++e) {
+        if (!weights[e] || !scales[e] || (reinterpret_cast<uintptr_t>(weights[e]) % 16) != 0) {
+            set_last_error("group table: weight %d is null or not 16-byte aligned", e);
+            return DSV3_ERR_INVALID_ARGUMENT;
+        }
+        CUtensorMap m;
+        const int rc = make_tmap(&m, weights[e], N, K, kPRows);
+        if (rc != DSV3_OK) return rc;
+        memcpy(maps + e, &m, sizeof(m));
+        sp[e] = scales[e];
+    }
+    DSV3_CUDA_TRY(cudaMemcpyAsync(table_dev, host.data(), host.size(), cudaMemcpyHostToDevice, stream));
+    DSV3_CUDA_TRY(cudaStreamSynchronize(stream));   // `host` goes out of scope
+    return DSV3_OK;
+}
+
+int launch_fp8_gemm_grouped(const void* table_dev, int n, const void* a, const float* a_s, const int* seg_dev,
+                            int64_t rows_total, int64_t N, int64_t K, void* c, cudaStream_t stream) {
+    if (rows_total <= 0 || N <= 0) return DSV3_OK;
+    if (!tc_supported(a, a, c, rows_total, N, K) || n <= 0 || n > kMaxGroups) {
+        set_last_error("grouped fp8_gemm: needs K %% 16 == 0, 16-byte aligned a and c, and 1..%d groups", kMaxGroups);
+        return DSV3_ERR_UNSUPPORTED;
+    }
+    const int kc = static_cast<int>((K + kChunk - 1) / kChunk);
+    if (kc > kScaleTabChunks) {
+        set_last_error("grouped fp8_gemm: K = %lld exceeds %d (scale table of the weight-major kernel)",
+                       static_cast<long long>(K), kScaleTabChunks * kChunk);
+        return DSV3_ERR_UNSUPPORTED;
+    }
+    const int64_t avg = (rows_total + n - 1) / n;          // the counts themselves live on the device
+    const int bn = avg <= 16 ? 16 : (avg <= 32 ? 32 : 64);
+    CUtensorMap tq, dummy;
+    int rc;
+    if ((rc = make_tmap(&tq, a, rows_total, K, bn)) != DSV3_OK) return rc;
+    memset(&dummy, 0, sizeof(dummy));
+    TcParams prm;
+    prm.a_s = a_s;
+    prm.b_s = nullptr;
+    prm.c = static_cast<__nv_bfloat16*>(c);
+    prm.tickets = nullptr;
+    prm.partials = nullptr;
+    prm.status = status_device_ptr();
+    if (!prm.status) return DSV3_ERR_CUDA;
+    prm.M = rows_total;
+    prm.N = N;
+    prm.kc = kc;
+    prm.tiles_p = static_cast<int>((N + kPRows - 1) / kPRows);
+    prm.tiles_q = 1;
+    prm.splits = 1;
+    prm.g_tmaps = static_cast<const CUtensorMap*>(table_dev);
+    prm.g_bs = reinterpret_cast<const float* const*>(static_cast<const uint8_t*>(table_dev) +
+                                                     static_cast<size_t>(n) * sizeof(CUtensorMap));
+    prm.g_seg = seg_dev;
+    prm.n_groups = n;
+    prm.g_slots = static_cast<int>((rows_total + bn - 1) / bn) + n;
+    const int64_t items = static_cast<int64_t>(prm.tiles_p) * prm.g_slots;
+    if (items >= (1ll << 31)) {
+        set_last_error("grouped fp8_gemm: too many work items");
+        return DSV3_ERR_UNSUPPORTED;
+    }
+    prm.num_items = static_cast<int>(items);
+    switch (bn) {
+        case 16: return launch_variant<16, true, 1>(dummy, tq, prm, stream);
+        case 32: return launch_variant<32, true, 1>(dummy, tq, prm, stream);
+        default: return launch_variant<64, true, 1>(dummy, tq, prm, stream);
+    }
 }
 
 }  // namespace dsv3

@@ -112,6 +112,37 @@ int dsv3_fp8_gemm_static(const void* a, const float* a_s, const void* b, const f
 int dsv3_set_gemm_policy(int kernel, int split_k);
 
 /*
+ * Grouped fp8_gemm over per-expert weights -- replaces the expert loop of MoE.forward
+ * (model.py:683-689: one act_quant + fp8_gemm triple per expert and two host synchronisations per
+ * expert) by one launch per projection.
+ *   table    : device buffer of dsv3_group_table_bytes(n) bytes, 64-byte aligned, filled once by
+ *              dsv3_group_table_build from host arrays of the n expert weight pointers (e4m3 [N, K] each)
+ *              and scale pointers (fp32 [ceil(N/128), ceil(K/128)] each); the call synchronises `stream`.
+ *   a, a_s   : e4m3 [rows_total, K] and fp32 [rows_total, ceil(K/128)]: the tokens routed to the experts,
+ *              sorted by expert
+ *   seg      : int32 [n + 1] in DEVICE memory: expert e owns rows [seg[e], seg[e+1]); rows at and
+ *              beyond seg[n] are ignored.  Nothing is read back to the host.
+ *   c        : bf16 [rows_total, N]; row r = a[r] @ weight[e(r)]^T with the block scales applied.
+ * Limits: n <= 256, K <= 18432, K % 16 == 0.
+ */
+size_t dsv3_group_table_bytes(int n_groups);
+int dsv3_group_table_build(void* table, const void* const* weights, const float* const* scales, int n_groups,
+                           int64_t N, int64_t K, dsv3_stream_t stream);
+int dsv3_fp8_gemm_grouped(const void* table, int n_groups, const void* a, const float* a_s, const int32_t* seg,
+                          int64_t rows_total, int64_t N, int64_t K, void* c, dsv3_stream_t stream);
+
+/*
+ * Scatter-add of the expert outputs -- the `y[idx] += expert(x[idx]) * weights[idx, top, None]` of
+ * model.py:689 for all experts at once, with the same bf16 rounding (product, then every partial sum) and
+ * the same ascending-expert order per token.
+ *   o   : bf16 [rows, dim] expert outputs        pos : int32 [T, topk], row of `o` for the token's j-th
+ *   w   : bf16 [T, topk] routing weights               smallest expert id, or -1 when that expert is not local
+ *   y   : bf16 [T, dim] (overwritten)            dim % 8 == 0
+ */
+int dsv3_moe_combine(const void* o, const int32_t* pos, const void* w, int64_t T, int topk, int64_t dim, void* y,
+                     dsv3_stream_t stream);
+
+/*
  * Harness weight quantiser (the reference ships only the inverse, weight_dequant;
  * the checkpoint format is described in README_WEIGHTS.md:60-92).
  *   w : bf16 [N, K] -> q : e4m3 [N, K], s : fp32 [ceil(N/128), ceil(K/128)]
