@@ -542,6 +542,150 @@ def run_detail(args):
     dsv3_b200.check_device_status()
 
 
+def run_moe_layer(args):
+    """BASELINE configs[2]: one DeepSeekMoE layer at V3 dims (dim 7168, 256 routed experts of moe_inter 2048,
+    sigmoid gate with bias, 8 groups / 4 kept, top-8, route_scale 2.5, one shared expert), T tokens.
+    Routed experts are sharded E/ws per rank and the routed output is all_reduced (model.py:658-666, 691-692).
+    Times the reference's expert loop (model.py:683-689, restated on the drop-in operators, with its host
+    synchronisations) and the grouped path; prints one JSON line."""
+    import torch
+    import torch.distributed as dist
+    import torch.nn.functional as F
+    import dsv3_b200
+    import kernel
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    torch.set_default_dtype(torch.bfloat16)
+    dim, inter, E, topk, n_groups, topk_groups, route_scale = 7168, 2048, args.moe_experts, 8, 8, 4, 2.5
+    T = args.moe_tokens
+    n_local = E // world
+    start = rank * n_local
+
+    class Lin:
+        scale_fmt = None
+
+        def __init__(self, N, K, gen):
+            w = (torch.randn(N, K, device=dev, dtype=torch.float32, generator=gen) * 0.02).to(torch.bfloat16)
+            self.weight, sc = dsv3_b200.weight_quant(w)
+            self.weight.scale = sc
+
+        def __call__(self, x):
+            xq, xs = kernel.act_quant(x)
+            return kernel.fp8_gemm(xq, xs, self.weight, self.weight.scale)
+
+    class Expert:
+        def __init__(self, d, i, gen):
+            self.w1, self.w2, self.w3 = Lin(i, d, gen), Lin(d, i, gen), Lin(i, d, gen)
+
+        def __call__(self, x):
+            return self.w2(F.silu(self.w1(x)) * self.w3(x))
+
+    class Layer:
+        pass
+
+    gen = torch.Generator(device=dev).manual_seed(1000 + rank)
+    shared_gen = torch.Generator(device=dev).manual_seed(77)
+    moe = Layer()
+    moe.dim, moe.n_routed_experts, moe.n_local_experts = dim, E, n_local
+    moe.experts_start_idx, moe.experts_end_idx = start, start + n_local
+    moe.experts = [Expert(dim, inter, gen) if start <= i < start + n_local else None for i in range(E)]
+    shared = Expert(dim, inter // world, shared_gen)       # column/row-parallel slice of the shared expert
+    gate_gen = torch.Generator(device=dev).manual_seed(5)
+    gate_w = (torch.randn(E, dim, device=dev, dtype=torch.float32, generator=gate_gen) * 0.02).to(torch.bfloat16)
+    gate_b = torch.randn(E, device=dev, dtype=torch.float32, generator=gate_gen) * 0.01
+
+    def gate(x):                                            # Gate.forward, model.py:566-598 (sigmoid + bias + groups)
+        scores = F.linear(x, gate_w).sigmoid()
+        original = scores
+        sc = (scores + gate_b).view(x.size(0), n_groups, -1)
+        group_scores = sc.topk(2, dim=-1)[0].sum(dim=-1)
+        idx = group_scores.topk(topk_groups, dim=-1)[1]
+        mask = sc.new_ones(x.size(0), n_groups, dtype=torch.bool).scatter_(1, idx, False)
+        sc = sc.masked_fill(mask.unsqueeze(-1), float("-inf")).flatten(1)
+        indices = torch.topk(sc, topk, dim=-1)[1]
+        weights = original.gather(1, indices)
+        weights = weights / weights.sum(dim=-1, keepdim=True) * route_scale
+        return weights.type_as(x), indices
+
+    def shared_experts(x):
+        z = shared(x)
+        if world > 1:
+            dist.all_reduce(z)
+        return z
+
+    moe.gate, moe.shared_experts = gate, shared_experts
+
+    def loop_forward(x):                                    # MoE.forward, model.py:669-693
+        weights, indices = moe.gate(x)
+        y = torch.zeros_like(x)
+        counts = torch.bincount(indices.flatten(), minlength=E).tolist()
+        for i in range(start, start + n_local):
+            if counts[i] == 0:
+                continue
+            idx, top = torch.where(indices == i)
+            y[idx] += moe.experts[i](x[idx]) * weights[idx, top, None]
+        z = moe.shared_experts(x)
+        if world > 1:
+            dist.all_reduce(y)
+        return y + z
+
+    def grouped_forward(x):
+        return dsv3_b200.grouped_moe_forward(moe, x, world_size=world)
+
+    xgen = torch.Generator(device=dev).manual_seed(9)
+    x = torch.randn(T, dim, device=dev, dtype=torch.float32, generator=xgen).to(torch.bfloat16)
+
+    def timeit(fn):
+        for _ in range(max(2, args.warmup)):
+            out = fn(x)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            out = fn(x)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.steps
+        if world > 1:
+            tt = torch.tensor([ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            ms = tt.item()
+        return ms, out
+
+    ms_loop, out_loop = timeit(loop_forward)
+    ms_grp, out_grp = timeit(grouped_forward)
+    dsv3_b200.check_device_status()
+    err = (out_grp.float() - out_loop.float()).abs()
+    rms = out_loop.float().pow(2).mean().sqrt()
+    ok = bool((err <= 2e-2 * (out_loop.float().abs() + rms)).all())
+    flops = 2.0 * 3 * dim * inter * (T * topk + T)           # routed pairs + shared expert
+    if rank == 0:
+        print(json.dumps({
+            "metric": "moe_layer_tokens_per_s", "value": T / (ms_grp * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(2, args.warmup), "ms_per_step": ms_grp, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 x fp8_e4m3 -> fp32", "data": "synthetic",
+            "config": {"workload": f"BASELINE configs[2]: DeepSeekMoE layer, dim {dim}, {E} routed experts (inter {inter}) "
+                                   f"+ 1 shared, top-{topk}, T={T} tokens, experts sharded {n_local} per rank"},
+            "grouped_ms": ms_grp, "expert_loop_ms": ms_loop, "speedup_vs_expert_loop": ms_loop / ms_grp,
+            "grouped_tflops": flops / (ms_grp * 1e-3) / 1e12, "agrees_with_expert_loop": ok,
+        }), flush=True)
+    if world > 1:
+        killer = threading.Timer(45.0, lambda: os._exit(0))
+        killer.daemon = True
+        killer.start()
+        dist.barrier()
+        dist.destroy_process_group()
+        killer.cancel()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -553,8 +697,13 @@ def main():
                     help="run one problem instead of the sweep (the case ncu captures are taken on)")
     ap.add_argument("--detail", action="store_true", help="per-(shape, M) table instead of the aggregate sweep")
     ap.add_argument("--detail-m", default=None, metavar="M1,M2,...", help="restrict --detail to these M values")
+    ap.add_argument("--moe-layer", action="store_true", help="BASELINE configs[2]: one MoE layer, expert loop vs grouped")
+    ap.add_argument("--moe-tokens", type=int, default=2048)
+    ap.add_argument("--moe-experts", type=int, default=256)
     args = ap.parse_args()
-    if args.single:
+    if args.moe_layer:
+        run_moe_layer(args)
+    elif args.single:
         run_single(args)
     elif args.detail:
         run_detail(args)

@@ -27,16 +27,25 @@ _memo = {"ref": None, "version": -1, "key": None, "value": None}
 stats = {"act_quant_calls": 0, "act_quant_reused": 0}
 
 
+def _version(x: torch.Tensor) -> int:
+    """In-place modification counter; tensors created under torch.inference_mode() have none, and there
+    the memo relies on object identity alone (model.py does not modify a projection's input in place)."""
+    try:
+        return x._version
+    except RuntimeError:
+        return -2
+
+
 def _quantised(x: torch.Tensor, block_size: int, scale_fmt: Optional[str]):
     ref = _memo["ref"]
     key = (x.data_ptr(), tuple(x.shape), block_size, scale_fmt)
-    if ref is not None and ref() is x and _memo["version"] == x._version and _memo["key"] == key:
+    if ref is not None and ref() is x and _memo["version"] == _version(x) and _memo["key"] == key:
         stats["act_quant_reused"] += 1
         return _memo["value"]
     value = act_quant(x, block_size, scale_fmt)
     stats["act_quant_calls"] += 1
     try:
-        _memo.update(ref=weakref.ref(x), version=x._version, key=key, value=value)
+        _memo.update(ref=weakref.ref(x), version=_version(x), key=key, value=value)
     except TypeError:           # tensor subclasses that cannot be weakly referenced: no memo
         _memo.update(ref=None, value=None)
     return value

@@ -42,6 +42,8 @@ def main() -> None:
     ap.add_argument("--prompt-len", type=int, default=128)
     ap.add_argument("--new-tokens", type=int, default=32)
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--seams", action="store_true",
+                    help="also run with dsv3_b200.install_linear / install_moe (shared quantisation, grouped MoE)")
     ap.add_argument("--out", default=None, help="write the result as JSON to this file")
     args = ap.parse_args()
 
@@ -151,6 +153,16 @@ def main() -> None:
     run(large, forced=tok_ref)
     lg_large, tok_large, _ = run(large, forced=tok_ref)
     use(ours)
+    seam = None
+    if args.seams:
+        orig_linear, orig_moe = M.linear, M.MoE.forward
+        dsv3_b200.install_linear(M)
+        dsv3_b200.install_moe(M)
+        run(ours, forced=tok_ref)
+        lg_seam, tok_seam, dt_seam = run(ours, forced=tok_ref)
+        dsv3_b200.check_device_status()
+        M.linear, M.MoE.forward = orig_linear, orig_moe
+        seam = (lg_seam, tok_seam, dt_seam)
 
     def rel_rms(a, b):
         return ((a - b).pow(2).mean().sqrt() / b.pow(2).mean().sqrt()).item()
@@ -169,6 +181,11 @@ def main() -> None:
         "decode_ms_per_step_reference_kernels": dt_ref * 1e3, "decode_ms_per_step_this_library": dt_ours * 1e3,
         "reference_noise_logits_rel_rms_max": max(noise), "reference_noise_greedy_token_match": noise_match,
         "logits_rel_rms_max_vs_reference_tile_16x32": vs_small, "logits_rel_rms_max_vs_reference_tile_64x128": vs_large,
+        "seams": None if seam is None else {
+            "logits_rel_rms_max_vs_reference": max(rel_rms(seam[0][i], lg_ref[i]) for i in range(lg_ref.size(0))),
+            "logits_rel_rms_max_vs_this_library_without_seams": max(rel_rms(seam[0][i], lg_ours[i]) for i in range(lg_ref.size(0))),
+            "greedy_token_match_vs_reference": (seam[1] == tok_ref).float().mean().item(),
+            "decode_ms_per_step": seam[2] * 1e3},
         "pass": bool(max(per_step) <= 2e-2 and match >= 0.99),
         "within_reference_noise": bool(max(per_step) <= 1.5 * max(noise) and match >= noise_match - 0.05),
     }
