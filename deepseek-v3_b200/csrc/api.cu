@@ -204,7 +204,8 @@ int dsv3_check_device_status(dsv3_stream_t stream, uint32_t detail[4]) {
     if (host[0] == 0) return DSV3_OK;
     const unsigned int zero[4] = {0, 0, 0, 0};
     DSV3_CUDA_TRY(cudaMemcpy(dptr, zero, sizeof(zero), cudaMemcpyHostToDevice));
-    set_last_error("device wait gave up: kind=%u (1 smem-empty, 2 smem-full, 3 tmem-empty, 4 tmem-full) chunk=%u cta=%u",
+    set_last_error("device wait gave up: kind=%u (1 smem-empty, 2 smem-full, 3 tmem-empty, 4 tmem-full, 5/6 group exchange, "
+                   "7/8 scale table) counter=%u cta=%u",
                    host[1], host[2], host[3]);
     return DSV3_ERR_DEVICE_TIMEOUT;
 }

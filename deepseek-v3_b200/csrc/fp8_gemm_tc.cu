@@ -130,7 +130,7 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, Cont
             } else if (now - t0 > kWaitLimitNs) {
                 ctl->abort_flag = 1;
                 if (atomicCAS(&status[0], 0u, 1u) == 0u) {
-                    status[1] = what;        // 1 empty, 2 full, 3 tmem-empty, 4 tmem-full
+                    status[1] = what;        // 1 empty, 2 full, 3 tmem-empty, 4 tmem-full, 5-6 exchange, 7-8 scale table
                     status[2] = g;           // chunk counter of the waiting role
                     status[3] = blockIdx.x;
                 }
