@@ -53,7 +53,6 @@ constexpr int kIssuers = 2;
 constexpr int kPromoThreads = 256;
 constexpr int kFirstPromoWarp = 4;
 constexpr int kGroupThreads = 128;        // one promotion group = 4 warps = all 128 TMEM lanes
-constexpr int kTwoGroupMinChunks = 48;    // K chunks per work item from which two promotion groups pay off
 // Register budget: 384 threads start with 168 each; the control warpgroup gives registers back and
 // the two promotion warpgroups take them (up to 128 accumulators + two 32-value load buffers).
 constexpr int kRegsControl = 40;
@@ -91,17 +90,26 @@ constexpr int kScaleTabChunks = 144;      // K chunks of one work item whose sca
 
 template <int BN, int G, bool kSwap>
 struct Cfg {
-    static constexpr int kStageBytes = kPRows * kChunk + BN * kChunk;
-    static constexpr int kExchangeBytes = (G == 2) ? kPRows * BN * 4 : 0;   // one group's accumulators, fp32
+    // The pipeline moves "units" of kUC consecutive K chunks: one smem stage, one TMEM stage and one
+    // round of hand-offs per unit.  Token-major tiles pair two chunks so that every hand-off (each costs
+    // several hundred cycles of latency) covers twice the tensor-core work.
+    static constexpr int kUC = kSwap ? 1 : 2;
+    static constexpr int kChunkBytes = kPRows * kChunk + BN * kChunk;      // P and Q tile of one chunk
+    static constexpr int kStageBytes = kUC * kChunkBytes;
+    static constexpr int kTmemUnits = kTmemStages / kUC;                    // unit products resident in TMEM
+    // two promotion groups: group 1 hands its sums over in rounds of kExchangeCols columns
+    static constexpr int kExchangeCols = 64;
+    static constexpr int kExchangeBytes = (G == 2) ? kPRows * kExchangeCols * 4 : 0;
     // weight-major tiles: a_s * b_s of the item's chunks for the tile's BN tokens, [chunk][token]
     static constexpr int kScaleTabBytes = kSwap ? kScaleTabChunks * BN * 4 : 0;
     static constexpr int kGroupTabBytes = kSwap ? 2048 : 0;   // grouped mode: token-tile prefix per group
     static constexpr int kStagesRaw = (232448 - 2048 - kExchangeBytes - kScaleTabBytes - kGroupTabBytes) / kStageBytes;
     static constexpr int kStages = kStagesRaw > 10 ? 10 : kStagesRaw;
     static constexpr int kTmemCols = kTmemStages * BN;  // 64..512, a power of two
-    // tiles + exchange buffer + barriers + control words + slack for the 1024-byte alignment of the tiles
+    // tiles + exchange buffer + tables + barriers + control words + slack for the 1024-byte alignment of the tiles
     static constexpr int kSmemBytes = kStages * kStageBytes + kExchangeBytes + kScaleTabBytes + kGroupTabBytes + 1024 + 1024;
     static_assert(kSmemBytes <= 232448, "shared memory per CTA");
+    static_assert(kStages >= 3, "at least three smem stages");
     static_assert(kTmemCols >= 32 && kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "TMEM columns");
     static_assert((BN * kChunk) % 1024 == 0, "Q tile must keep 1024-byte alignment");
     // more than half of an SM's shared memory, so two CTAs can never share an SM (and its TMEM)
@@ -232,7 +240,8 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
                    const TcParams p) {
     using C = Cfg<BN, G, kSwap>;
     constexpr int NS = C::kStages;
-    constexpr int NT = kTmemStages;
+    constexpr int UC = C::kUC;           // K chunks per pipeline unit
+    constexpr int NT = C::kTmemUnits;    // TMEM stages, in units
     constexpr int CPT = BN * G / 2;   // accumulator columns per promotion thread
     constexpr int kWriters = (G == 2) ? kGroupThreads : kPromoThreads;   // threads that write results
     static_assert(kSwap || BN == 128, "token-major tiles are 128 x 128 (one b_s value per tile and chunk)");
@@ -303,7 +312,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
     tc_fence_after();
     const uint32_t tmem_base = ctl->tmem_base;
 
-    if constexpr (G == 2) {
+    if constexpr (G == 2 || !kSwap) {
         if (warp < kFirstPromoWarp) {
             asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsControl));
         } else {
@@ -323,15 +332,20 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
                 const int q_row = kSwap ? it.row0 : it.q_idx * BN;
                 const void* map_p = (kSwap && p.n_groups > 0) ? static_cast<const void*>(p.g_tmaps + it.group)
                                                                : static_cast<const void*>(&tmap_p);
-                for (int ch = it.c0; ch < it.c1; ++ch, ++g) {
+                const int n_units = (it.c1 - it.c0 + UC - 1) / UC;
+                for (int u = 0; u < n_units; ++u, ++g) {
                     const int s = g % NS;
                     ok = wait_probed(probe, empty_bar(s), ((g / NS) & 1u) ^ 1u, ctl, p.status, 1, g);
                     if (!ok) break;
                     probe = mbar_test_wait(empty_bar((g + 1) % NS), (((g + 1) / NS) & 1u) ^ 1u) ? 1u : 0u;
-                    const uint32_t dst = tiles + s * C::kStageBytes;
-                    mbar_arrive_expect_tx(full_bar(s), C::kStageBytes);
-                    tma_load_2d(dst, map_p, ch * kChunk, p_row, full_bar(s));
-                    tma_load_2d(dst + kPRows * kChunk, &tmap_q, ch * kChunk, q_row, full_bar(s));
+                    const int k0 = it.c0 + u * UC;
+                    const int nch = min(UC, it.c1 - k0);
+                    mbar_arrive_expect_tx(full_bar(s), nch * C::kChunkBytes);
+                    for (int j = 0; j < nch; ++j) {
+                        const uint32_t dst = tiles + s * C::kStageBytes + j * C::kChunkBytes;
+                        tma_load_2d(dst, map_p, (k0 + j) * kChunk, p_row, full_bar(s));
+                        tma_load_2d(dst + kPRows * kChunk, &tmap_q, (k0 + j) * kChunk, q_row, full_bar(s));
+                    }
                 }
             }
         }
@@ -345,29 +359,33 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
             bool ok = true;
             for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
                 const Item it = decode_item<BN, kSwap>(item, p, g_prefix);
-                for (int ch = it.c0; ch < it.c1; ++ch, ++g) {
+                const int n_units = (it.c1 - it.c0 + UC - 1) / UC;
+                for (int u = 0; u < n_units; ++u, ++g) {
                     if (g % kIssuers != me) continue;
                     const int s = g % NS, ts = g % NT;
                     ok = wait_probed(probe_t, tempty_bar(ts), ((g / NT) & 1u) ^ 1u, ctl, p.status, 3, g) &&
                          wait_probed(probe_f, full_bar(s), (g / NS) & 1u, ctl, p.status, 2, g);
                     if (!ok) break;
-                    {   // probe this issuer's next chunk now; the answers are read one iteration later
+                    {   // probe this issuer's next unit now; the answers are read one iteration later
                         const uint32_t gn = g + kIssuers;
                         probe_t = mbar_test_wait(tempty_bar(gn % NT), ((gn / NT) & 1u) ^ 1u) ? 1u : 0u;
                         probe_f = mbar_test_wait(full_bar(gn % NS), (gn / NS) & 1u) ? 1u : 0u;
                     }
                     tc_fence_after();
-                    const uint32_t sp = tiles + s * C::kStageBytes;
-                    const uint64_t dp = umma_desc_k_major_sw128(sp);
-                    const uint64_t dq = umma_desc_k_major_sw128(sp + kPRows * kChunk);
-                    const uint32_t d_tmem = tmem_base + ts * BN;
+                    const int nch = min(UC, it.c1 - it.c0 - u * UC);
+                    for (int j = 0; j < nch; ++j) {
+                        const uint32_t sp = tiles + s * C::kStageBytes + j * C::kChunkBytes;
+                        const uint64_t dp = umma_desc_k_major_sw128(sp);
+                        const uint64_t dq = umma_desc_k_major_sw128(sp + kPRows * kChunk);
+                        const uint32_t d_tmem = tmem_base + (ts * UC + j) * BN;   // one TMEM region per chunk
 #pragma unroll
-                    for (int k = 0; k < kChunk / 32; ++k) {
-                        // 32 bytes further along K inside the 128-byte swizzle atom: +2 in address units of 16 B
-                        tc_mma_f8(d_tmem, dp + 2u * k, dq + 2u * k, idesc, k > 0 ? 1u : 0u);
+                        for (int k = 0; k < kChunk / 32; ++k) {
+                            // 32 bytes further along K inside the 128-byte swizzle atom: +2 in address units of 16 B
+                            tc_mma_f8(d_tmem, dp + 2u * k, dq + 2u * k, idesc, k > 0 ? 1u : 0u);
+                        }
                     }
                     tc_commit(empty_bar(s));   // smem stage reusable once these MMAs have read it
-                    tc_commit(tfull_bar(ts));  // chunk product complete in TMEM
+                    tc_commit(tfull_bar(ts));  // the unit's chunk products are complete in TMEM
                 }
             }
         }
@@ -392,29 +410,28 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
         // while the previous step's FMAs issue.
         constexpr int HC = (CPT >= 32) ? 32 : CPT;
         constexpr int SPC = CPT / HC;
-        constexpr int U = SPC > 2 ? SPC : 2;   // steps per trip of the pipelined loop (static register indices)
-        uint32_t probe = 0;   // result of test_wait on tfull[] for this group's next chunk
-        // Issues (does not wait for) the load of step `st` of chunk `gg`; the first step of a chunk
-        // first waits for the chunk's product to be complete in TMEM.
-        auto issue_load = [&](uint32_t gg, int st, uint32_t* v) -> bool {
-            const int ts = gg % NT;
-            if (st == 0) {
-                const bool mine = wait_probed(probe, tfull_bar(ts), (gg / NT) & 1u, ctl, p.status, 4, gg);
+        uint32_t probe = 0;   // result of test_wait on tfull[] for this group's next unit
+        // Issues (does not wait for) the load of step `st` of chunk `j` of unit `gu`; the first step of a
+        // unit first waits for the unit's products to be complete in TMEM.
+        auto issue_load = [&](uint32_t gu, int j, int st, uint32_t* v) -> bool {
+            const int ts = gu % NT;
+            if (j == 0 && st == 0) {
+                const bool mine = wait_probed(probe, tfull_bar(ts), (gu / NT) & 1u, ctl, p.status, 4, gu);
                 if (!__all_sync(0xffffffffu, mine)) return false;
-                probe = mbar_test_wait(tfull_bar((gg + G) % NT), ((gg + G) / NT) & 1u) ? 1u : 0u;
+                probe = mbar_test_wait(tfull_bar((gu + G) % NT), ((gu + G) / NT) & 1u) ? 1u : 0u;
                 tc_fence_after();
             }
-            tmem_load_cols<HC>(t_lane + ts * BN + st * HC, v);
+            tmem_load_cols<HC>(t_lane + (ts * UC + j) * BN + st * HC, v);
             return true;
         };
-        // Completes the outstanding load; after the last step of a chunk the TMEM stage goes back
-        // to the MMA issuer.
-        auto finish_load = [&](uint32_t gg, int st) {
+        // Completes the outstanding load; `last` = it was the last load of the unit, whose TMEM stage
+        // then goes back to the MMA issuers.
+        auto finish_load = [&](uint32_t gu, bool last) {
             tc_wait_ld();
-            if (st == SPC - 1) {
+            if (last) {
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(tempty_bar(gg % NT));
+                if (lane == 0) mbar_arrive(tempty_bar(gu % NT));
             }
         };
 
@@ -460,17 +477,18 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
                     if (!ok) break;
                 }
             }
-            // this group's chunks of the item: local indices first, first + G, ...
+            // this group's units of the item: local unit indices first, first + G, ...
+            const int n_units = (n_ch + UC - 1) / UC;
             const int first = (G == 1 || (g & 1u) == static_cast<uint32_t>(grp)) ? 0 : 1;
-            const int n_mine = n_ch > first ? (n_ch - first + G - 1) / G : 0;
-            const int n_steps = n_mine * SPC;
-            auto chunk_g = [&](int mc) -> uint32_t { return g + first + G * mc; };     // pipeline counter
-            auto chunk_k = [&](int mc) -> int { return it.c0 + first + G * mc; };      // K chunk index
-            // scale of this group's mc-th chunk for this thread's row (token-major tiles); clamped so
-            // that the look-ahead never leaves the item
-            auto row_scale = [&](int mc) -> float {
-                const int c = min(chunk_k(mc), it.c1 - 1);
-                return __ldg(as_ptr + c) * __ldg(bs_ptr + c);
+            const int n_mine = n_units > first ? (n_units - first + G - 1) / G : 0;          // units of this group
+            auto unit_g = [&](int mu) -> uint32_t { return g + first + G * mu; };            // pipeline counter
+            auto unit_k = [&](int mu) -> int { return it.c0 + UC * (first + G * mu); };      // first K chunk of the unit
+            auto unit_n = [&](int mu) -> int { return min(UC, it.c1 - unit_k(mu)); };        // chunks in the unit
+            // scale of K chunk c for this thread's row (token-major tiles); clamped so that the
+            // look-ahead never leaves the item
+            auto row_scale = [&](int c) -> float {
+                const int cc = min(c, it.c1 - 1);
+                return __ldg(as_ptr + cc) * __ldg(bs_ptr + cc);
             };
             // acc[off ..] += v * (a_s * b_s) for K chunk ch; v holds HC columns starting at column 2*off
             auto fold = [&](int ch, const uint32_t* v, float sc, auto off_c) {
@@ -490,43 +508,139 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
                 }
             };
 
-            // Software pipeline over the load steps of this group's chunks, two register buffers.  One
-            // trip covers U steps: one chunk when SPC >= 2, two chunks when SPC == 1.  Row scales
-            // (global memory) are fetched two of the group's chunks ahead of their use.
-            uint32_t va[HC], vb[HC];
-            float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f;
-            if constexpr (!kSwap) {
-                s0 = row_scale(0);
-                s1 = row_scale(1);
+            // Software pipeline over the load steps, two register buffers: while the FMAs of one step issue,
+            // the TMEM load of the next step is in flight.
+            constexpr bool kBatched = (UC == 2 && G == 1);
+            uint32_t va[kBatched ? 1 : HC], vb[kBatched ? 1 : HC];
+            uint32_t va64[kBatched ? 64 : 1], vb64[kBatched ? 64 : 1];
+            if constexpr (kBatched) {
+                if (n_mine > 0) {   // first unit of the item: wait and start its first load here
+                    const uint32_t gu = unit_g(0);
+                    const bool mine = wait_probed(probe, tfull_bar(gu % NT), (gu / NT) & 1u, ctl, p.status, 4, gu);
+                    ok = __all_sync(0xffffffffu, mine);
+                    if (ok) {
+                        probe = mbar_test_wait(tfull_bar((gu + 1) % NT), ((gu + 1) / NT) & 1u) ? 1u : 0u;
+                        tc_fence_after();
+                        tc_ld_x64(t_lane + ((gu % NT) * UC) * BN, va64);
+                    }
+                }
+            } else {
+                if (n_mine > 0) ok = issue_load(unit_g(0), 0, 0, va);
             }
-            if (n_steps > 0) ok = issue_load(chunk_g(0), 0, va);
-            // step u of the trip starting at step t: finish its load, start the next one, fold
-            auto step = [&](int t, auto u_c, uint32_t* cur, uint32_t* nxt) {
-                constexpr int u = decltype(u_c)::value;
-                constexpr int st = u % SPC;
-                const int T = t + u;
-                if (!ok || T >= n_steps) return;
-                const int mc = T / SPC;
-                finish_load(chunk_g(mc), st);
-                if (T + 1 < n_steps) ok = issue_load(chunk_g((T + 1) / SPC), (u + 1) % SPC, nxt);
-                if constexpr (!kSwap) {
-                    if (st == 0) s2 = row_scale(mc + 2);
+            if constexpr (UC == 2 && G == 1) {
+                // ---- token-major tiles, all eight warps on every unit: a thread reads its 64 columns of both
+                // chunks of the unit in one batch (tcgen05.wait::ld has no per-load granularity, so one wait
+                // per unit exposes the TMEM latency once), returns the TMEM stage at once and only then does
+                // the FMAs; the other promotion warp of the scheduler overlaps with them.  Row scales (global
+                // memory) are fetched one unit ahead.
+                static_assert(CPT == 64, "token-major tiles: 64 columns per thread");
+                float sa0 = row_scale(unit_k(0)), sa1 = row_scale(unit_k(0) + 1);     // this unit's two chunks
+                for (int mu = 0; ok && mu < n_mine; ++mu) {
+                    const uint32_t gu = unit_g(mu);
+                    const int ts = gu % NT;
+                    const int nch = unit_n(mu);
+                    if (mu > 0) {
+                        const bool mine = wait_probed(probe, tfull_bar(ts), (gu / NT) & 1u, ctl, p.status, 4, gu);
+                        ok = __all_sync(0xffffffffu, mine);
+                        if (!ok) break;
+                        probe = mbar_test_wait(tfull_bar((gu + 1) % NT), ((gu + 1) / NT) & 1u) ? 1u : 0u;
+                        tc_fence_after();
+                    }
+                    const uint32_t taddr = t_lane + (ts * UC) * BN;
+                    if (mu > 0) tc_ld_x64(taddr, va64);
+                    if (nch > 1) tc_ld_x64(taddr + BN, vb64);
+                    float sb0 = 0.0f, sb1 = 0.0f;
+                    if (mu + 1 < n_mine) {
+                        sb0 = row_scale(unit_k(mu + 1));
+                        sb1 = row_scale(unit_k(mu + 1) + 1);
+                    }
+                    tc_wait_ld();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(tempty_bar(ts));
+                    {
+                        const float2 sc2 = make_float2(sa0, sa0);
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            acc[j] = __ffma2_rn(make_float2(__uint_as_float(va64[2 * j]), __uint_as_float(va64[2 * j + 1])),
+                                                sc2, acc[j]);
+                    }
+                    if (nch > 1) {
+                        const float2 sc2 = make_float2(sa1, sa1);
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            acc[j] = __ffma2_rn(make_float2(__uint_as_float(vb64[2 * j]), __uint_as_float(vb64[2 * j + 1])),
+                                                sc2, acc[j]);
+                    }
+                    sa0 = sb0;
+                    sa1 = sb1;
                 }
-                fold(chunk_k(mc), cur, s0, std::integral_constant<int, st * (HC / 2)>{});
-                if (st == SPC - 1) {   // next chunk of the group
-                    s0 = s1;
-                    s1 = s2;
+            } else if constexpr (UC == 2) {
+                // ---- token-major tiles, two promotion groups: one trip = one unit = 2 chunks x SPC steps;
+                // step u -> chunk u / SPC, column step u % SPC (all static).  Row scales are fetched one unit ahead.
+                constexpr int U = 2 * SPC;
+                float sa0 = row_scale(unit_k(0)), sa1 = row_scale(unit_k(0) + 1);     // this unit's two chunks
+                float sb0 = 0.0f, sb1 = 0.0f;                                          // next unit's
+                auto step = [&](int mu, auto u_c, uint32_t* cur, uint32_t* nxt) {
+                    constexpr int u = decltype(u_c)::value;
+                    constexpr int j = u / SPC, st = u % SPC;
+                    const int nch = unit_n(mu);
+                    if (!ok || j >= nch) return;
+                    const bool last_of_unit = (st == SPC - 1) && (j == nch - 1);
+                    finish_load(unit_g(mu), last_of_unit);
+                    // the step after this one: same chunk, next chunk of the unit, or the next unit of the group
+                    if (st + 1 < SPC) {
+                        ok = issue_load(unit_g(mu), j, st + 1, nxt);
+                    } else if (j + 1 < nch) {
+                        ok = issue_load(unit_g(mu), j + 1, 0, nxt);
+                    } else if (mu + 1 < n_mine) {
+                        ok = issue_load(unit_g(mu + 1), 0, 0, nxt);
+                    }
+                    if (u == 0 && mu + 1 < n_mine) {
+                        sb0 = row_scale(unit_k(mu + 1));
+                        sb1 = row_scale(unit_k(mu + 1) + 1);
+                    }
+                    fold(unit_k(mu) + j, cur, j == 0 ? sa0 : sa1, std::integral_constant<int, st * (HC / 2)>{});
+                };
+                for (int mu = 0; ok && mu < n_mine; ++mu) {
+                    step(mu, std::integral_constant<int, 0>{}, va, vb);
+                    step(mu, std::integral_constant<int, 1>{}, vb, va);
+                    step(mu, std::integral_constant<int, 2>{}, va, vb);
+                    step(mu, std::integral_constant<int, 3>{}, vb, va);
+                    if constexpr (U == 8) {
+                        step(mu, std::integral_constant<int, 4>{}, va, vb);
+                        step(mu, std::integral_constant<int, 5>{}, vb, va);
+                        step(mu, std::integral_constant<int, 6>{}, va, vb);
+                        step(mu, std::integral_constant<int, 7>{}, vb, va);
+                    }
+                    sa0 = sb0;
+                    sa1 = sb1;
                 }
-            };
-            for (int t = 0; ok && t < n_steps; t += U) {
-                step(t, std::integral_constant<int, 0>{}, va, vb);
-                step(t, std::integral_constant<int, 1>{}, vb, va);
-                if constexpr (U == 4) {
-                    step(t, std::integral_constant<int, 2>{}, va, vb);
-                    step(t, std::integral_constant<int, 3>{}, vb, va);
+                static_assert(U == 4 || U == 8, "token-major tiles: 64 or 128 columns per thread");
+            } else {
+                // ---- weight-major tiles: a unit is one chunk; one trip covers max(2, SPC) steps
+                constexpr int U = SPC > 2 ? SPC : 2;
+                const int n_steps = n_mine * SPC;
+                auto step = [&](int t, auto u_c, uint32_t* cur, uint32_t* nxt) {
+                    constexpr int u = decltype(u_c)::value;
+                    constexpr int st = u % SPC;
+                    const int T = t + u;
+                    if (!ok || T >= n_steps) return;
+                    const int mu = T / SPC;
+                    finish_load(unit_g(mu), st == SPC - 1);
+                    if (T + 1 < n_steps) ok = issue_load(unit_g((T + 1) / SPC), 0, (u + 1) % SPC, nxt);
+                    fold(unit_k(mu), cur, 0.0f, std::integral_constant<int, st * (HC / 2)>{});
+                };
+                for (int t = 0; ok && t < n_steps; t += U) {
+                    step(t, std::integral_constant<int, 0>{}, va, vb);
+                    step(t, std::integral_constant<int, 1>{}, vb, va);
+                    if constexpr (U == 4) {
+                        step(t, std::integral_constant<int, 2>{}, va, vb);
+                        step(t, std::integral_constant<int, 3>{}, vb, va);
+                    }
                 }
             }
-            g += n_ch;
+            g += n_units;
             if (!ok) break;
             if constexpr (kSwap) {
                 mbar_arrive(tab_free_bar);   // this thread is done reading the scale table
@@ -534,25 +648,35 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
 
             // ---------------------------------------------------- combine the two groups' sums
             float* accf = reinterpret_cast<float*>(acc);
-            const uint32_t ex_phase = item_no & 1u;
             if constexpr (G == 2) {
-              if (grp == 1) {
-                bool mine = bounded_wait(exch_free_bar, ex_phase ^ 1u, ctl, p.status, 5, item_no);
-                ok = __all_sync(0xffffffffu, mine);
-                if (!ok) break;
+                // the buffer holds kExchangeCols columns: CPT / kExchangeCols rounds per item, each one phase
+                // of the two exchange barriers
+                constexpr int XC = C::kExchangeCols;
+                constexpr int kRounds = CPT / XC;
+                static_assert(CPT % XC == 0, "exchange rounds");
+                bool done_group1 = false;
 #pragma unroll
-                for (int j = 0; j < CPT; ++j) exch[j * kPRows + row] = accf[j];
-                mbar_arrive(exch_full_bar);
-                continue;   // group 0 writes the result
-              }
-              {
-                bool mine = bounded_wait(exch_full_bar, ex_phase, ctl, p.status, 6, item_no);
-                ok = __all_sync(0xffffffffu, mine);
-                if (!ok) break;
+                for (int r = 0; r < kRounds; ++r) {
+                    const uint32_t ex_phase = (item_no * kRounds + r) & 1u;
+                    if (grp == 1) {
+                        bool mine = bounded_wait(exch_free_bar, ex_phase ^ 1u, ctl, p.status, 5, item_no);
+                        ok = __all_sync(0xffffffffu, mine);
+                        if (!ok) break;
 #pragma unroll
-                for (int j = 0; j < CPT; ++j) accf[j] += exch[j * kPRows + row];
-                mbar_arrive(exch_free_bar);
-              }
+                        for (int j = 0; j < XC; ++j) exch[j * kPRows + row] = accf[r * XC + j];
+                        mbar_arrive(exch_full_bar);
+                        done_group1 = true;
+                    } else {
+                        bool mine = bounded_wait(exch_full_bar, ex_phase, ctl, p.status, 6, item_no);
+                        ok = __all_sync(0xffffffffu, mine);
+                        if (!ok) break;
+#pragma unroll
+                        for (int j = 0; j < XC; ++j) accf[r * XC + j] += exch[j * kPRows + row];
+                        mbar_arrive(exch_free_bar);
+                    }
+                }
+                if (!ok) break;
+                if (done_group1) continue;   // group 0 writes the result
             }
 
             // ---------------------------------------------------- write-out (group 0)
@@ -869,8 +993,6 @@ int launch_fp8_gemm_tc(const void* a, const float* a_s, const void* b, const flo
     } else if (pl.bn == 128) {
         // long K: two promotion groups on alternate chunks; short K: the end-of-tile combine would
         // cost more than it saves
-        const int chunks_per_item = pl.kc / pl.splits;
-        if (chunks_per_item >= kTwoGroupMinChunks) return launch_variant<128, false, 2>(tp, tq, prm, stream);
         return launch_variant<128, false, 1>(tp, tq, prm, stream);
     }
     set_last_error("fp8_gemm: no tcgen05 variant for tile width %d", pl.bn);
