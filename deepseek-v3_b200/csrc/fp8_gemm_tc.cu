@@ -104,7 +104,10 @@ struct Cfg {
     static constexpr int kScaleTabBytes = kSwap ? kScaleTabChunks * BN * 4 : 0;
     static constexpr int kGroupTabBytes = kSwap ? 2048 : 0;   // grouped mode: token-tile prefix per group
     static constexpr int kStagesRaw = (232448 - 2048 - kExchangeBytes - kScaleTabBytes - kGroupTabBytes) / kStageBytes;
-    static constexpr int kStages = kStagesRaw > 10 ? 10 : kStagesRaw;
+    static constexpr int kStagesCap = kStagesRaw > 10 ? 10 : kStagesRaw;
+    // weight-major tiles: an even stage count, so that a stage always belongs to the same MMA issuer and
+    // the issuer may probe its next full[] barrier (see the issuer loop)
+    static constexpr int kStages = kSwap ? (kStagesCap & ~1) : kStagesCap;
     static constexpr int kTmemCols = kTmemStages * BN;  // 64..512, a power of two
     // tiles + exchange buffer + tables + barriers + control words + slack for the 1024-byte alignment of the tiles
     static constexpr int kSmemBytes = kStages * kStageBytes + kExchangeBytes + kScaleTabBytes + kGroupTabBytes + 1024 + 1024;
@@ -355,7 +358,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
             constexpr uint32_t idesc = umma_idesc_e4m3_f32(kPRows, BN);
             const uint32_t me = static_cast<uint32_t>(warp - 1);
             uint32_t g = 0;
-            uint32_t probe_t = 0, probe_f = 0;   // probes of tempty[] / full[] for this issuer's next chunk
+            uint32_t probe_t = 0, probe_f = 0;   // probes of tempty[] / full[] for this issuer's next unit
             bool ok = true;
             for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
                 const Item it = decode_item<BN, kSwap>(item, p, g_prefix);
@@ -363,13 +366,19 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
                 for (int u = 0; u < n_units; ++u, ++g) {
                     if (g % kIssuers != me) continue;
                     const int s = g % NS, ts = g % NT;
+                    constexpr bool kProbeFull = (NS % kIssuers) == 0;
                     ok = wait_probed(probe_t, tempty_bar(ts), ((g / NT) & 1u) ^ 1u, ctl, p.status, 3, g) &&
-                         wait_probed(probe_f, full_bar(s), (g / NS) & 1u, ctl, p.status, 2, g);
+                         wait_probed(kProbeFull ? probe_f : 0u, full_bar(s), (g / NS) & 1u, ctl, p.status, 2, g);
                     if (!ok) break;
-                    {   // probe this issuer's next unit now; the answers are read one iteration later
+                    {   // Probe the TMEM stage of this issuer's next unit now; the answer is read one iteration
+                        // later.  A parity probe is only meaningful if the barrier's previous phase is known to be
+                        // complete: true for tempty (NT is even, so a stage always belongs to the same issuer, which
+                        // waited for that phase itself); for full[] only when NS is even as well (otherwise the previous
+                        // phase of that stage belongs to the other issuer and the barrier is always waited for).
+                        static_assert(NT % kIssuers == 0, "a TMEM stage must always be used by the same issuer");
                         const uint32_t gn = g + kIssuers;
                         probe_t = mbar_test_wait(tempty_bar(gn % NT), ((gn / NT) & 1u) ^ 1u) ? 1u : 0u;
-                        probe_f = mbar_test_wait(full_bar(gn % NS), (gn / NS) & 1u) ? 1u : 0u;
+                        if constexpr (kProbeFull) probe_f = mbar_test_wait(full_bar(gn % NS), (gn / NS) & 1u) ? 1u : 0u;
                     }
                     tc_fence_after();
                     const int nch = min(UC, it.c1 - it.c0 - u * UC);
@@ -519,7 +528,6 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
                     const bool mine = wait_probed(probe, tfull_bar(gu % NT), (gu / NT) & 1u, ctl, p.status, 4, gu);
                     ok = __all_sync(0xffffffffu, mine);
                     if (ok) {
-                        probe = mbar_test_wait(tfull_bar((gu + 1) % NT), ((gu + 1) / NT) & 1u) ? 1u : 0u;
                         tc_fence_after();
                         tc_ld_x64(t_lane + ((gu % NT) * UC) * BN, va64);
                     }
@@ -543,7 +551,6 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
                         const bool mine = wait_probed(probe, tfull_bar(ts), (gu / NT) & 1u, ctl, p.status, 4, gu);
                         ok = __all_sync(0xffffffffu, mine);
                         if (!ok) break;
-                        probe = mbar_test_wait(tfull_bar((gu + 1) % NT), ((gu + 1) / NT) & 1u) ? 1u : 0u;
                         tc_fence_after();
                     }
                     const uint32_t taddr = t_lane + (ts * UC) * BN;
@@ -558,6 +565,9 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(tempty_bar(ts));
+                    // probe the next unit now: its answer is needed only after the FMAs below, by which time
+                    // the probe has long returned (and the unit's MMAs, issued a unit ago, are usually complete)
+                    probe = mbar_test_wait(tfull_bar((gu + 1) % NT), ((gu + 1) / NT) & 1u) ? 1u : 0u;
                     {
                         const float2 sc2 = make_float2(sa0, sa0);
 #pragma unroll
