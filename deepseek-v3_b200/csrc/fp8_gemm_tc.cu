@@ -69,7 +69,7 @@ struct TcParams {
     const float* a_s;
     const float* b_s;
     __nv_bfloat16* c;
-    float* partials;        // [splits][M][N] fp32, only when splits > 1
+    float* partials;        // [splits][tiles][bn / 4][128] float4 (padded partial tiles), only when splits > 1
     int* tickets;           // one per tile, zero on entry and on exit
     unsigned int* status;   // device status words
     int64_t M, N;
@@ -86,7 +86,10 @@ struct TcParams {
     int g_slots;                   // upper bound on the number of token tiles over all groups
 };
 
-constexpr int kScaleTabChunks = 144;      // K chunks of one work item whose scales fit the shared-memory table (K <= 18432)
+// K chunks of one weight-major work item whose scales fit the shared-memory table: 144 (K <= 18432) for
+// 16- and 32-token tiles, 72 for 64-token tiles (the same 18 KB, which leaves room for eight 24 KB stages;
+// longer K is split, or uses the 32-token variant in grouped mode)
+constexpr int scale_tab_chunks(int bn) { return bn >= 64 ? 72 : 144; }
 
 template <int BN, int G, bool kSwap>
 struct Cfg {
@@ -101,7 +104,7 @@ struct Cfg {
     static constexpr int kExchangeCols = 64;
     static constexpr int kExchangeBytes = (G == 2) ? kPRows * kExchangeCols * 4 : 0;
     // weight-major tiles: a_s * b_s of the item's chunks for the tile's BN tokens, [chunk][token]
-    static constexpr int kScaleTabBytes = kSwap ? kScaleTabChunks * BN * 4 : 0;
+    static constexpr int kScaleTabBytes = kSwap ? scale_tab_chunks(BN) * BN * 4 : 0;
     static constexpr int kGroupTabBytes = kSwap ? 2048 : 0;   // grouped mode: token-tile prefix per group
     static constexpr int kStagesRaw = (232448 - 2048 - kExchangeBytes - kScaleTabBytes - kGroupTabBytes) / kStageBytes;
     static constexpr int kStagesCap = kStagesRaw > 10 ? 10 : kStagesRaw;
@@ -122,7 +125,7 @@ struct Cfg {
 struct Control {
     volatile uint32_t abort_flag;
     uint32_t tmem_base;
-    volatile int ticket;
+    volatile int ticket[2];
 };
 
 // Waits for the phase with the given parity.  The common case costs one or a few try_wait
@@ -286,7 +289,8 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
         mbar_init(tab_ready_bar, kPromoThreads);
         mbar_init(tab_free_bar, kPromoThreads);
         ctl->abort_flag = 0;
-        ctl->ticket = 0;
+        ctl->ticket[0] = 0;
+        ctl->ticket[1] = 0;
         mbar_fence_init();
         tma_prefetch_desc(&tmap_p);
         tma_prefetch_desc(&tmap_q);
@@ -692,7 +696,66 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
             // ---------------------------------------------------- write-out (group 0)
             // normal: thread = token row, CPT consecutive output columns
             // swap  : thread = output column (weight row), CPT tokens
-            if (p.splits == 1) {
+            bool write_out = true;
+            if (p.splits > 1) {
+                // Split-K: park the partial sums, take a ticket; the last arrival of the tile sums the
+                // partial tiles in split order (deterministic) and writes the result.  Partial tiles use a
+                // private layout chosen for coalescing, [split][tile][group of 4 columns][128 rows] float4:
+                // a warp (32 consecutive rows, one column group) moves 512 contiguous bytes, and rows and
+                // columns beyond M or N are stored like the rest, so nothing here is predicated and the
+                // compiler is free to keep a whole batch of loads in flight.
+                constexpr int kTileVec = BN * kPRows / 4;
+                const int64_t split_stride = static_cast<int64_t>(p.tiles_p) * p.tiles_q * kTileVec;
+                float4* tile_part = reinterpret_cast<float4*>(p.partials) + static_cast<int64_t>(it.tile) * kTileVec +
+                                    (col0 / 4) * kPRows + row;
+                {
+                    float4* dst = tile_part + it.split * split_stride;
+#pragma unroll
+                    for (int j = 0; j < CPT / 4; ++j)
+                        __stcg(dst + j * kPRows, make_float4(accf[4 * j], accf[4 * j + 1], accf[4 * j + 2], accf[4 * j + 3]));
+                }
+                // Release: the barrier orders every writer's stores before the ticket thread's fence, which
+                // is cumulative.  The ticket slot alternates between items, so the next item's ticket cannot
+                // overwrite this one before every thread has read it (a barrier of the next item lies between).
+                const int slot = static_cast<int>(item_no & 1u);
+                promo_barrier<kWriters>();
+                if (threadIdx.x == kFirstPromoWarp * 32) {
+                    __threadfence();
+                    const int t = atomicAdd(p.tickets + it.tile, 1);
+                    if (t == p.splits - 1) p.tickets[it.tile] = 0;  // last arrival: leave the ticket clean
+                    __threadfence();                                 // acquire side for the reads below
+                    ctl->ticket[slot] = t;
+                }
+                promo_barrier<kWriters>();
+                write_out = (ctl->ticket[slot] == p.splits - 1);
+                if (write_out) {
+#pragma unroll
+                    for (int j = 0; j < CPT; ++j) accf[j] = 0.0f;
+                    constexpr int kBatch = (CPT >= 64) ? 1 : 64 / CPT;   // splits whose loads are in flight together (64 registers)
+                    for (int sp0 = 0; sp0 < p.splits; sp0 += kBatch) {
+                        float4 t4[kBatch][CPT / 4];
+#pragma unroll
+                        for (int bi = 0; bi < kBatch; ++bi) {
+                            const float4* src = tile_part + min(sp0 + bi, p.splits - 1) * split_stride;
+#pragma unroll
+                            for (int j = 0; j < CPT / 4; ++j) t4[bi][j] = __ldcg(src + j * kPRows);
+                        }
+#pragma unroll
+                        for (int bi = 0; bi < kBatch; ++bi) {
+                            if (sp0 + bi < p.splits) {
+#pragma unroll
+                                for (int j = 0; j < CPT / 4; ++j) {
+                                    accf[4 * j] += t4[bi][j].x;
+                                    accf[4 * j + 1] += t4[bi][j].y;
+                                    accf[4 * j + 2] += t4[bi][j].z;
+                                    accf[4 * j + 3] += t4[bi][j].w;
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+            if (write_out) {
                 if constexpr (!kSwap) {
                     if (p_row < M) {
                         __nv_bfloat16* crow = p.c + p_row * N;
@@ -717,97 +780,6 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
                         for (int j = 0; j < CPT; ++j) {
                             const int64_t m = q_base + j;
                             if (m < m_end) p.c[m * N + p_row] = __float2bfloat16_rn(accf[j]);
-                        }
-                    }
-                }
-            } else {
-                // split-K: park the partial sums, take a ticket, the last arrival of the tile reduces
-                float* part = p.partials + static_cast<int64_t>(it.split) * M * N;
-                const bool vec4 = (N % 4) == 0;
-                if constexpr (!kSwap) {
-                    if (p_row < M) {
-#pragma unroll
-                        for (int j = 0; j < CPT; j += 4) {
-                            const int64_t n = q_base + j;
-                            if (vec4 && n + 4 <= N) {
-                                __stcg(reinterpret_cast<float4*>(part + p_row * N + n),
-                                       make_float4(accf[j], accf[j + 1], accf[j + 2], accf[j + 3]));
-                            } else {
-#pragma unroll
-                                for (int e = 0; e < 4; ++e)
-                                    if (n + e < N) __stcg(part + p_row * N + n + e, accf[j + e]);
-                            }
-                        }
-                    }
-                } else {
-                    if (p_row < N) {
-#pragma unroll
-                        for (int j = 0; j < CPT; ++j) {
-                            const int64_t m = q_base + j;
-                            if (m < m_end) __stcg(part + m * N + p_row, accf[j]);
-                        }
-                    }
-                }
-                __threadfence();
-                promo_barrier<kWriters>();
-                if (threadIdx.x == kFirstPromoWarp * 32) {
-                    const int t = atomicAdd(p.tickets + it.tile, 1);
-                    if (t == p.splits - 1) p.tickets[it.tile] = 0;  // last arrival: leave the ticket clean
-                    ctl->ticket = t;
-                }
-                promo_barrier<kWriters>();
-                const bool last = (ctl->ticket == p.splits - 1);
-                promo_barrier<kWriters>();  // everyone has read the ticket before the next item overwrites it
-                if (last) {
-                    __threadfence();
-                    // sum in split order (deterministic); every trip keeps CPT independent loads in flight
-#pragma unroll
-                    for (int j = 0; j < CPT; ++j) accf[j] = 0.0f;
-                    // (the loop is unrolled so that the loads of four splits are in flight together; the
-                    //  additions still happen in split order)
-#pragma unroll 4
-                    for (int sp = 0; sp < p.splits; ++sp) {
-                        const float* ps = p.partials + static_cast<int64_t>(sp) * M * N;
-                        if constexpr (!kSwap) {
-                            if (p_row < M) {
-#pragma unroll
-                                for (int j = 0; j < CPT; j += 4) {
-                                    const int64_t n = q_base + j;
-                                    if (vec4 && n + 4 <= N) {
-                                        const float4 t4 = __ldcg(reinterpret_cast<const float4*>(ps + p_row * N + n));
-                                        accf[j] += t4.x; accf[j + 1] += t4.y; accf[j + 2] += t4.z; accf[j + 3] += t4.w;
-                                    } else {
-#pragma unroll
-                                        for (int e = 0; e < 4; ++e)
-                                            if (n + e < N) accf[j + e] += __ldcg(ps + p_row * N + n + e);
-                                    }
-                                }
-                            }
-                        } else {
-                            if (p_row < N) {
-#pragma unroll
-                                for (int j = 0; j < CPT; ++j) {
-                                    const int64_t m = q_base + j;
-                                    if (m < m_end) accf[j] += __ldcg(ps + m * N + p_row);
-                                }
-                            }
-                        }
-                    }
-                    if constexpr (!kSwap) {
-                        if (p_row < M) {
-#pragma unroll
-                            for (int j = 0; j < CPT; ++j) {
-                                const int64_t n = q_base + j;
-                                if (n < N) p.c[p_row * N + n] = __float2bfloat16_rn(accf[j]);
-                            }
-                        }
-                    } else {
-                        if (p_row < N) {
-#pragma unroll
-                            for (int j = 0; j < CPT; ++j) {
-                                const int64_t m = q_base + j;
-                                if (m < m_end) p.c[m * N + p_row] = __float2bfloat16_rn(accf[j]);
-                            }
                         }
                     }
                 }
@@ -912,33 +884,40 @@ TcPlan tc_plan(int64_t M, int64_t N, int64_t K, int force_kernel, int force_spli
     }
     const int64_t tiles = static_cast<int64_t>(pl.tiles_p) * pl.tiles_q;
     int splits = 1;
+    const int tab = pl.swap ? scale_tab_chunks(pl.bn) : (1 << 30);   // chunks per item the scale table holds
     if (force_split > 0) {
         splits = force_split;
-    } else if (pl.swap) {
-        // Weight-streaming regime.  Splitting K fills idle SMs but every split item pays a fence + ticket
-        // + reduction round in its epilogue.  Cost model fitted to B200 measurements (microseconds):
-        //   rounds(S) * chunks_per_item(S) * 0.42  +  (S > 1 ? 4.0 : 0)
-        // with rounds = ceil(tiles * S / SMs); the factor with the lowest estimate wins (ties: fewer splits).
+    } else if (tiles <= kMaxTickets) {
+        // Splitting K fills idle SMs, but every split item pays for parking its partial tile, a fence and a
+        // ticket, and the last arrival of a tile sums the partial tiles.  Estimate, fitted to B200
+        // measurements (microseconds; the launch's fixed cost is the same for every factor and left out):
+        //   rounds(S) * (chunks_per_item(S) * c + (S > 1 ? e0 + e1 * S : 0)),   rounds = ceil(tiles * S / SMs)
+        // with c the time per K chunk of one CTA, never below the time the whole problem needs at HBM
+        // bandwidth.  The factor with the lowest estimate wins (ties: fewer splits).
         const int sms = num_sms();
+        const double c = pl.swap ? (pl.bn == 64 ? 0.30 : 0.22) : 0.26;
+        const double e0 = pl.swap ? 1.0 : 2.3, e1 = pl.swap ? 0.2 * pl.bn / 64.0 : 0.5;
+        const double hbm_floor = (static_cast<double>(N) * K + static_cast<double>(M) * K) / 6.0e6;
         double best = 1e30;
         for (int sfac = 1; sfac <= 8 && sfac <= pl.kc; ++sfac) {
-            const int64_t rounds = (tiles * sfac + sms - 1) / sms;
             const int per_item = (pl.kc + sfac - 1) / sfac;
-            const double t = static_cast<double>(rounds) * per_item * 0.42 + (sfac > 1 ? 4.0 : 0.0);
+            if (per_item > tab) continue;
+            const int64_t rounds = (tiles * sfac + sms - 1) / sms;
+            double t = static_cast<double>(rounds) * per_item * c;
+            if (t < hbm_floor) t = hbm_floor;
+            if (sfac > 1) t += static_cast<double>(rounds) * (e0 + e1 * sfac);
             if (t < best - 1e-9) {
                 best = t;
                 splits = sfac;
             }
         }
     }
-    // Token-major tiles (M > 64) are never split: measured on B200, the partial-sum round trip costs
-    // more than the idle SMs it would fill (e.g. M=256, N=2048, K=7168: 31 us unsplit, 53 us at 4 splits).
     if (splits > pl.kc) splits = pl.kc;
     if (splits < 1) splits = 1;
     if (tiles > kMaxTickets) splits = 1;
-    if (pl.swap && (pl.kc + splits - 1) / splits > kScaleTabChunks) {
-        // the weight-major kernel keeps an item's scales in a shared-memory table of kScaleTabChunks chunks
-        splits = (pl.kc + kScaleTabChunks - 1) / kScaleTabChunks;
+    if ((pl.kc + splits - 1) / splits > tab) {
+        // the weight-major kernel keeps an item's scales in a shared-memory table
+        splits = (pl.kc + tab - 1) / tab;
         if (splits > 32 || tiles > kMaxTickets) {   // absurdly long K: use token-major tiles instead
             TcPlan alt = tc_plan(M, N, K, 2, 1);
             return alt;
@@ -950,7 +929,11 @@ TcPlan tc_plan(int64_t M, int64_t N, int64_t K, int force_kernel, int force_spli
 
 size_t tc_workspace_bytes(const TcPlan& pl, int64_t M, int64_t N) {
     if (pl.splits <= 1) return 0;
-    return static_cast<size_t>(DSV3_WORKSPACE_HEADER_BYTES) + static_cast<size_t>(pl.splits) * M * N * sizeof(float);
+    // one padded tile (128 x bn fp32) per (split, tile)
+    (void)M;
+    (void)N;
+    return static_cast<size_t>(DSV3_WORKSPACE_HEADER_BYTES) +
+           static_cast<size_t>(pl.splits) * pl.tiles_p * pl.tiles_q * kPRows * pl.bn * sizeof(float);
 }
 
 int launch_fp8_gemm_tc(const void* a, const float* a_s, const void* b, const float* b_s, int64_t M, int64_t N,
@@ -1053,13 +1036,14 @@ int launch_fp8_gemm_grouped(const void* table_dev, int n, const void* a, const f
         return DSV3_ERR_UNSUPPORTED;
     }
     const int kc = static_cast<int>((K + kChunk - 1) / kChunk);
-    if (kc > kScaleTabChunks) {
+    if (kc > scale_tab_chunks(32)) {
         set_last_error("grouped fp8_gemm: K = %lld exceeds %d (scale table of the weight-major kernel)",
-                       static_cast<long long>(K), kScaleTabChunks * kChunk);
+                       static_cast<long long>(K), scale_tab_chunks(32) * kChunk);
         return DSV3_ERR_UNSUPPORTED;
     }
     const int64_t avg = (rows_total + n - 1) / n;          // the counts themselves live on the device
-    const int bn = avg <= 16 ? 16 : (avg <= 32 ? 32 : 64);
+    int bn = avg <= 16 ? 16 : (avg <= 32 ? 32 : 64);
+    if (kc > scale_tab_chunks(bn)) bn = 32;                // the 64-token variant's table is shorter
     CUtensorMap tq, dummy;
     int rc;
     if ((rc = make_tmap(&tq, a, rows_total, K, bn)) != DSV3_OK) return rc;
