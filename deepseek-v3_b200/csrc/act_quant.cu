@@ -66,6 +66,8 @@ __device__ __forceinline__ uint2 quant8(const uint4& v, float s) {
 // block_size == 128.  nblk = rows * K / 128; block b covers elements [128 b, 128 b + 128).
 __global__ void __launch_bounds__(kThreads, 4) act_quant128_kernel(const uint4* __restrict__ x, uint2* __restrict__ y,
                                                                  float* __restrict__ s, int64_t nblk, int scale_fmt) {
+    griddep_launch_dependents();   // a dependent launch (the GEMM) may set itself up while this kernel runs
+    griddep_wait();
     const int lane16 = threadIdx.x & 15;
     const int64_t hw = (static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x) >> 4;  // global half-warp id
     const int64_t nhw = (static_cast<int64_t>(gridDim.x) * kThreads) >> 4;
@@ -100,6 +102,8 @@ __global__ void __launch_bounds__(kThreads, 4) act_quant128_kernel(const uint4* 
 __global__ void __launch_bounds__(kThreads) act_quant_generic_kernel(const uint4* __restrict__ x,
                                                                       uint2* __restrict__ y, float* __restrict__ s,
                                                                       int64_t nblk, int groups, int scale_fmt) {
+    griddep_launch_dependents();
+    griddep_wait();
     const int lane = threadIdx.x & 31;
     const int64_t warp = (static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x) >> 5;
     const int64_t nwarps = (static_cast<int64_t>(gridDim.x) * kThreads) >> 5;
@@ -135,14 +139,15 @@ int launch_act_quant(const void* x, int64_t rows, int64_t K, int block_size, int
         const int64_t per_cta = (kThreads / 16) * kUnroll;
         int64_t grid = (nblk + per_cta - 1) / per_cta;
         if (grid > cap) grid = cap;
-        act_quant128_kernel<<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
-            static_cast<const uint4*>(x), static_cast<uint2*>(y), s, nblk, scale_fmt);
+        DSV3_CUDA_TRY(launch_dependent(act_quant128_kernel, dim3(static_cast<unsigned>(grid)), dim3(kThreads), 0, stream,
+                                       static_cast<const uint4*>(x), static_cast<uint2*>(y), s, nblk, scale_fmt));
     } else {
         const int64_t per_cta = kThreads / 32;
         int64_t grid = (nblk + per_cta - 1) / per_cta;
         if (grid > cap) grid = cap;
-        act_quant_generic_kernel<<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
-            static_cast<const uint4*>(x), static_cast<uint2*>(y), s, nblk, block_size / 8, scale_fmt);
+        DSV3_CUDA_TRY(launch_dependent(act_quant_generic_kernel, dim3(static_cast<unsigned>(grid)), dim3(kThreads), 0, stream,
+                                       static_cast<const uint4*>(x), static_cast<uint2*>(y), s, nblk, block_size / 8,
+                                       scale_fmt));
     }
     DSV3_CUDA_TRY(cudaGetLastError());
     return DSV3_OK;

@@ -3,6 +3,8 @@
 #include <cstdio>
 #include <cstring>
 
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "gemm_plan.cuh"
 
@@ -41,6 +43,11 @@ int num_sms() {
         cached[dev] = n;
     }
     return cached[dev];
+}
+
+bool pdl_enabled() {
+    static const bool on = (getenv("DSV3_DISABLE_PDL") == nullptr);
+    return on;
 }
 
 // ------------------------------------------------------------------ status words

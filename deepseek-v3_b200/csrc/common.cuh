@@ -17,6 +17,26 @@ namespace dsv3 {
 void set_last_error(const char* fmt, ...);
 int cuda_fail(cudaError_t e, const char* what);  // records detail, returns DSV3_ERR_CUDA
 int num_sms();                                   // SM count of the current device (cached)
+bool pdl_enabled();                              // programmatic dependent launch (off when DSV3_DISABLE_PDL is set)
+
+// Launches `kern` so that it may be scheduled while the kernel before it in the stream is still draining
+// (programmatic stream serialisation).  Such a kernel must execute griddep_wait() before it reads or
+// writes anything a predecessor may touch.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_dependent(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
 
 #define DSV3_CUDA_TRY(expr)                                         \
     do {                                                            \
@@ -113,6 +133,16 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
 }
 
 // ---------------------------------------------------------------- PTX: TMA
+// Programmatic dependent launch.  wait: blocks until every kernel this launch depends on has completed and
+// its memory is visible (returns at once for an ordinary launch).  launch_dependents: the next kernel in
+// the stream may start being scheduled; it still waits, in its own griddep_wait(), for this grid to finish.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Brings one box of a tiled tensor into L2 (no shared-memory destination, no completion to wait for).
+__device__ __forceinline__ void tma_prefetch_l2_2d(const void* tmap, int x, int y) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(tmap), "r"(x), "r"(y) : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }

@@ -296,6 +296,19 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
         tma_prefetch_desc(&tmap_q);
     }
     if (warp == 1) tc_alloc(smem_u32(&ctl->tmem_base), C::kTmemCols);
+    // Programmatic dependent launch: nothing above touches global memory, so it may overlap the tail of
+    // the kernel before this one in the stream.  While waiting for that kernel, the producer thread pulls
+    // the first weight boxes of this CTA's first work item into L2 (L2 is the point of coherence: should
+    // the predecessor still be writing those weights, the later TMA loads see its data all the same).
+    if (threadIdx.x == 0 && p.n_groups == 0 && static_cast<int>(blockIdx.x) < p.num_items) {
+        const Item it = decode_item<BN, kSwap>(blockIdx.x, p, g_prefix);
+        const void* wmap = kSwap ? static_cast<const void*>(&tmap_p) : static_cast<const void*>(&tmap_q);
+        const int wrow = kSwap ? it.p_idx * kPRows : it.q_idx * BN;
+        const int n_pre = min(it.c1 - it.c0, NS * UC);
+        for (int j = 0; j < n_pre; ++j) tma_prefetch_l2_2d(wmap, (it.c0 + j) * kChunk, wrow);
+    }
+    griddep_launch_dependents();
+    griddep_wait();
     if constexpr (kSwap) {
         if (p.n_groups > 0) {
             // token tiles per group, then an exclusive prefix sum (n_groups <= kMaxGroups)
@@ -857,8 +870,7 @@ int launch_variant(const CUtensorMap& tp, const CUtensorMap& tq, const TcParams&
         configured[dev] = true;
     }
     int grid = prm.num_items < num_sms() ? prm.num_items : num_sms();
-    kern<<<grid, kNumThreads, C::kSmemBytes, stream>>>(tp, tq, prm);
-    DSV3_CUDA_TRY(cudaGetLastError());
+    DSV3_CUDA_TRY(launch_dependent(kern, dim3(grid), dim3(kNumThreads), C::kSmemBytes, stream, tp, tq, prm));
     return DSV3_OK;
 }
 
