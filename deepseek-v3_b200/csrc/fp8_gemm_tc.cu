@@ -76,6 +76,8 @@ struct TcParams {
     int kc;                 // number of K chunks
     int tiles_p, tiles_q;
     int splits;
+    int raster;             // token-major tiles: P tiles (token tiles) that share consecutive Q tiles in the work order
+    int tma_store;          // token-major tiles: results leave through shared memory and a TMA store (needs N % 8 == 0)
     int num_items;          // tiles_p * tiles_q * splits
     // Grouped mode (MoE experts; weight-major tiles only, no split-K): group e multiplies the activation
     // rows [g_seg[e], g_seg[e+1]) with its own weight.  n_groups == 0 means one ordinary GEMM.
@@ -106,14 +108,18 @@ struct Cfg {
     // weight-major tiles: a_s * b_s of the item's chunks for the tile's BN tokens, [chunk][token]
     static constexpr int kScaleTabBytes = kSwap ? scale_tab_chunks(BN) * BN * 4 : 0;
     static constexpr int kGroupTabBytes = kSwap ? 2048 : 0;   // grouped mode: token-tile prefix per group
-    static constexpr int kStagesRaw = (232448 - 2048 - kExchangeBytes - kScaleTabBytes - kGroupTabBytes) / kStageBytes;
+    // token-major tiles: the 128 x 128 bf16 result tile is staged here (two 128-byte-swizzled 128 x 64 boxes)
+    static constexpr int kStoreBytes = (!kSwap && G == 1) ? kPRows * 128 * 2 : 0;
+    static constexpr int kStagesRaw =
+        (232448 - 2048 - kStoreBytes - kExchangeBytes - kScaleTabBytes - kGroupTabBytes) / kStageBytes;
     static constexpr int kStagesCap = kStagesRaw > 10 ? 10 : kStagesRaw;
     // weight-major tiles: an even stage count, so that a stage always belongs to the same MMA issuer and
     // the issuer may probe its next full[] barrier (see the issuer loop)
     static constexpr int kStages = kSwap ? (kStagesCap & ~1) : kStagesCap;
     static constexpr int kTmemCols = kTmemStages * BN;  // 64..512, a power of two
     // tiles + exchange buffer + tables + barriers + control words + slack for the 1024-byte alignment of the tiles
-    static constexpr int kSmemBytes = kStages * kStageBytes + kExchangeBytes + kScaleTabBytes + kGroupTabBytes + 1024 + 1024;
+    static constexpr int kSmemBytes =
+        kStages * kStageBytes + kStoreBytes + kExchangeBytes + kScaleTabBytes + kGroupTabBytes + 1024 + 1024;
     static_assert(kSmemBytes <= 232448, "shared memory per CTA");
     static_assert(kStages >= 3, "at least three smem stages");
     static_assert(kTmemCols >= 32 && kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "TMEM columns");
@@ -203,7 +209,7 @@ __device__ __forceinline__ Item decode_item(int item, const TcParams& p, const i
     it.tile = item / p.splits;
     it.split = item - it.tile * p.splits;
     // grouped raster: 8 P-tiles share consecutive Q-tiles so a wave re-uses both operands in L2
-    constexpr int kGroup = 8;
+    const int kGroup = p.raster;
     const int per_group = kGroup * p.tiles_q;
     const int grp = it.tile / per_group;
     const int first_p = grp * kGroup;
@@ -243,7 +249,7 @@ __device__ __forceinline__ void promo_barrier() { asm volatile("bar.sync 1, %0;"
 template <int BN, bool kSwap, int G>
 __global__ void __launch_bounds__(kNumThreads, 1)
 fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constant__ CUtensorMap tmap_q,
-                   const TcParams p) {
+                   const __grid_constant__ CUtensorMap tmap_c, const TcParams p) {
     using C = Cfg<BN, G, kSwap>;
     constexpr int NS = C::kStages;
     constexpr int UC = C::kUC;           // K chunks per pipeline unit
@@ -256,10 +262,12 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t tiles = (raw + 1023u) & ~1023u;
     uint8_t* gen_tiles = smem_raw + (tiles - raw);
-    float* exch = reinterpret_cast<float*>(gen_tiles + NS * C::kStageBytes);   // [column][row] fp32
-    float* sc_tab = reinterpret_cast<float*>(gen_tiles + NS * C::kStageBytes + C::kExchangeBytes);   // [chunk][token]
-    int* g_prefix = reinterpret_cast<int*>(gen_tiles + NS * C::kStageBytes + C::kExchangeBytes + C::kScaleTabBytes);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(gen_tiles + NS * C::kStageBytes + C::kExchangeBytes + C::kScaleTabBytes +
+    uint8_t* store_buf = gen_tiles + NS * C::kStageBytes;                       // 1024-byte aligned (swizzle atom)
+    uint8_t* after_store = store_buf + C::kStoreBytes;
+    float* exch = reinterpret_cast<float*>(after_store);   // [column][row] fp32
+    float* sc_tab = reinterpret_cast<float*>(after_store + C::kExchangeBytes);   // [chunk][token]
+    int* g_prefix = reinterpret_cast<int*>(after_store + C::kExchangeBytes + C::kScaleTabBytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(after_store + C::kExchangeBytes + C::kScaleTabBytes +
                                                  C::kGroupTabBytes);
     Control* ctl = reinterpret_cast<Control*>(bars + 2 * NS + 2 * NT + 4);
     const uint32_t bar0 = smem_u32(bars);
@@ -294,6 +302,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
         mbar_fence_init();
         tma_prefetch_desc(&tmap_p);
         tma_prefetch_desc(&tmap_q);
+        if (!kSwap && p.tma_store) tma_prefetch_desc(&tmap_c);
     }
     if (warp == 1) tc_alloc(smem_u32(&ctl->tmem_base), C::kTmemCols);
     // Programmatic dependent launch: nothing above touches global memory, so it may overlap the tail of
@@ -770,7 +779,32 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
             }
             if (write_out) {
                 if constexpr (!kSwap) {
-                    if (p_row < M) {
+                    if (C::kStoreBytes > 0 && p.tma_store) {
+                        // The four warps of a column half stage their 128 x 64 bf16 box in shared memory (128-byte
+                        // swizzle: 16-byte slot c of row r sits at slot c ^ (r & 7), which also keeps the
+                        // vector stores free of bank conflicts) and one thread hands it to the TMA, which clips
+                        // rows beyond M and columns beyond N.  The store of the previous tile is only known to
+                        // have read the buffer once its issuer has waited for it, hence the first barrier.
+                        static_assert(CPT == 64 || C::kStoreBytes == 0, "one 128-byte box row per thread");
+                        const int half = (warp - kFirstPromoWarp) >> 2;
+                        uint8_t* sbuf = store_buf + half * (kPRows * 128);
+                        const bool issuer = ((threadIdx.x & 127) == 0);
+                        if (issuer) bulk_wait_group_read0();
+                        asm volatile("bar.sync %0, 128;" ::"r"(2 + half) : "memory");
+#pragma unroll
+                        for (int cidx = 0; cidx < CPT / 8; ++cidx) {
+                            const int j = cidx * 8;
+                            const uint4 o = make_uint4(pack_bf16x2(accf[j], accf[j + 1]), pack_bf16x2(accf[j + 2], accf[j + 3]),
+                                                       pack_bf16x2(accf[j + 4], accf[j + 5]), pack_bf16x2(accf[j + 6], accf[j + 7]));
+                            *reinterpret_cast<uint4*>(sbuf + row * 128 + ((cidx ^ (row & 7)) << 4)) = o;
+                        }
+                        fence_proxy_async_shared();
+                        asm volatile("bar.sync %0, 128;" ::"r"(2 + half) : "memory");
+                        if (issuer) {
+                            tma_store_2d(&tmap_c, smem_u32(sbuf), it.q_idx * BN + half * 64, it.p_idx * kPRows);
+                            bulk_commit_group();
+                        }
+                    } else if (p_row < M) {
                         __nv_bfloat16* crow = p.c + p_row * N;
                         const bool vec_ok = (N % 8) == 0;
 #pragma unroll
@@ -801,6 +835,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
     }
 
     // ---------------------------------------------------------------- teardown
+    if (!kSwap && warp >= kFirstPromoWarp && (threadIdx.x & 127) == 0) bulk_wait_group0();   // result tiles have left shared memory
     __syncwarp();
     tc_fence_before();
     __syncthreads();
@@ -858,8 +893,31 @@ int make_tmap(CUtensorMap* map, const void* base, int64_t rows, int64_t K, int b
     return DSV3_OK;
 }
 
+// Result matrix [M, N] bf16, row-major; box = 64 columns (128 bytes) x 128 rows, 128-byte swizzle.
+int make_tmap_out(CUtensorMap* map, void* base, int64_t M, int64_t N) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) {
+        set_last_error("cuTensorMapEncodeTiled is not available from the driver");
+        return DSV3_ERR_CUDA;
+    }
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(M)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(N) * 2};
+    const cuuint32_t box[2] = {64, static_cast<cuuint32_t>(kPRows)};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_last_error("cuTensorMapEncodeTiled (result matrix) failed with CUresult %d (M=%lld N=%lld)", static_cast<int>(r),
+                       static_cast<long long>(M), static_cast<long long>(N));
+        return DSV3_ERR_CUDA;
+    }
+    return DSV3_OK;
+}
+
 template <int BN, bool kSwap, int G>
-int launch_variant(const CUtensorMap& tp, const CUtensorMap& tq, const TcParams& prm, cudaStream_t stream) {
+int launch_variant(const CUtensorMap& tp, const CUtensorMap& tq, const CUtensorMap& tc, const TcParams& prm,
+                   cudaStream_t stream) {
     using C = Cfg<BN, G, kSwap>;
     auto kern = fp8_gemm_tc_kernel<BN, kSwap, G>;
     static bool configured[64] = {};
@@ -870,7 +928,7 @@ int launch_variant(const CUtensorMap& tp, const CUtensorMap& tq, const TcParams&
         configured[dev] = true;
     }
     int grid = prm.num_items < num_sms() ? prm.num_items : num_sms();
-    DSV3_CUDA_TRY(launch_dependent(kern, dim3(grid), dim3(kNumThreads), C::kSmemBytes, stream, tp, tq, prm));
+    DSV3_CUDA_TRY(launch_dependent(kern, dim3(grid), dim3(kNumThreads), C::kSmemBytes, stream, tp, tq, tc, prm));
     return DSV3_OK;
 }
 
@@ -959,14 +1017,18 @@ int launch_fp8_gemm_tc(const void* a, const float* a_s, const void* b, const flo
             return DSV3_ERR_WORKSPACE;
         }
     }
-    CUtensorMap tp, tq;
+    CUtensorMap tp, tq, tc;
+    memset(&tc, 0, sizeof(tc));
     int rc;
+    bool tma_store = false;
     if (pl.swap) {
         if ((rc = make_tmap(&tp, b, N, K, kPRows)) != DSV3_OK) return rc;
         if ((rc = make_tmap(&tq, a, M, K, pl.bn)) != DSV3_OK) return rc;
     } else {
         if ((rc = make_tmap(&tp, a, M, K, kPRows)) != DSV3_OK) return rc;
         if ((rc = make_tmap(&tq, b, N, K, pl.bn)) != DSV3_OK) return rc;
+        tma_store = (N % 8) == 0;   // row pitch of the result must be a multiple of 16 bytes for a tensor map
+        if (tma_store && (rc = make_tmap_out(&tc, c, M, N)) != DSV3_OK) return rc;
     }
     TcParams prm;
     prm.a_s = a_s;
@@ -983,6 +1045,15 @@ int launch_fp8_gemm_tc(const void* a, const float* a_s, const void* b, const flo
     prm.tiles_p = pl.tiles_p;
     prm.tiles_q = pl.tiles_q;
     prm.splits = pl.splits;
+    prm.tma_store = tma_store ? 1 : 0;
+    // Work order: `raster` token tiles share consecutive weight tiles.  For token-major tiles the group is
+    // made as tall as keeps its activations (raster x 128 x K bytes) within about a quarter of L2, so that
+    // the weights are streamed from HBM as few times as possible.
+    prm.raster = 8;
+    if (!pl.swap) {
+        const int64_t fit = (32ll << 20) / (static_cast<int64_t>(kPRows) * K);
+        prm.raster = static_cast<int>(fit < 8 ? 8 : (fit > 64 ? 64 : fit));
+    }
     prm.num_items = pl.tiles_p * pl.tiles_q * pl.splits;
     prm.g_tmaps = nullptr;
     prm.g_bs = nullptr;
@@ -991,14 +1062,14 @@ int launch_fp8_gemm_tc(const void* a, const float* a_s, const void* b, const flo
     prm.g_slots = 0;
     if (pl.swap) {
         switch (pl.bn) {
-            case 16: return launch_variant<16, true, 1>(tp, tq, prm, stream);
-            case 32: return launch_variant<32, true, 1>(tp, tq, prm, stream);
-            case 64: return launch_variant<64, true, 1>(tp, tq, prm, stream);
+            case 16: return launch_variant<16, true, 1>(tp, tq, tc, prm, stream);
+            case 32: return launch_variant<32, true, 1>(tp, tq, tc, prm, stream);
+            case 64: return launch_variant<64, true, 1>(tp, tq, tc, prm, stream);
         }
     } else if (pl.bn == 128) {
         // long K: two promotion groups on alternate chunks; short K: the end-of-tile combine would
         // cost more than it saves
-        return launch_variant<128, false, 1>(tp, tq, prm, stream);
+        return launch_variant<128, false, 1>(tp, tq, tc, prm, stream);
     }
     set_last_error("fp8_gemm: no tcgen05 variant for tile width %d", pl.bn);
     return DSV3_ERR_UNSUPPORTED;
@@ -1074,6 +1145,8 @@ int launch_fp8_gemm_grouped(const void* table_dev, int n, const void* a, const f
     prm.tiles_p = static_cast<int>((N + kPRows - 1) / kPRows);
     prm.tiles_q = 1;
     prm.splits = 1;
+    prm.raster = 8;
+    prm.tma_store = 0;
     prm.g_tmaps = static_cast<const CUtensorMap*>(table_dev);
     prm.g_bs = reinterpret_cast<const float* const*>(static_cast<const uint8_t*>(table_dev) +
                                                      static_cast<size_t>(n) * sizeof(CUtensorMap));
@@ -1087,9 +1160,9 @@ int launch_fp8_gemm_grouped(const void* table_dev, int n, const void* a, const f
     }
     prm.num_items = static_cast<int>(items);
     switch (bn) {
-        case 16: return launch_variant<16, true, 1>(dummy, tq, prm, stream);
-        case 32: return launch_variant<32, true, 1>(dummy, tq, prm, stream);
-        default: return launch_variant<64, true, 1>(dummy, tq, prm, stream);
+        case 16: return launch_variant<16, true, 1>(dummy, tq, dummy, prm, stream);
+        case 32: return launch_variant<32, true, 1>(dummy, tq, dummy, prm, stream);
+        default: return launch_variant<64, true, 1>(dummy, tq, dummy, prm, stream);
     }
 }
 
