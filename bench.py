@@ -105,6 +105,13 @@ def gemm_bytes(M, N, K):
     return M * K + N * K + 4 * M * kc + 4 * (-(-N // 128)) * kc + 2 * M * N
 
 
+# ncu captures of one launch each (commands and figures in the named summaries): measured DRAM bytes,
+# the (M, N, K) of the captured problem, the summary file.
+NCU_TRAFFIC = {
+    "token_major": (163.02e6 + 132.05e6, (4096, 18432, 7168), "profiles/fp8_gemm_tc_token_major_4096x18432x7168.md"),
+    "weight_major": (117.66e6 + 3.94e6, (8, 7168, 16384), "profiles/fp8_gemm_tc_weight_major_8x7168x16384.md"),
+}
+
 def read_peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -348,23 +355,49 @@ def run_ours(args):
     h2d = sum(M * K * 2 for _, K, _, M, _ in plan)
     d2h = sum(M * N * 2 for _, _, N, M, _ in plan)
 
-    def e2e_step():
-        for name, K, N, M, ar in plan:
-            wq, ws = weights[name]
-            x = hx[K][:M].to(dev, non_blocking=True)
-            xq, xs = kernel.act_quant(x)
-            y = kernel.fp8_gemm(xq, xs, wq, ws)
-            if ar:
-                dist.all_reduce(y)
-            hy[: M * N].view(M, N).copy_(y, non_blocking=True)
+    # Three streams, the way a host program would pipeline the public API: activations go up on one,
+    # act_quant + fp8_gemm run on the second, results come down on the third (PCIe is full duplex), with
+    # two device-side input buffers so that an upload can run ahead of the GEMM that consumes the other.
+    s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+    Kmax = max(acts)
+    xbuf = [torch.empty(Mmax * Kmax, device=dev, dtype=torch.bfloat16) for _ in range(2)]
 
-    e2e_step()
+    def e2e_step():
+        done = [None, None]      # event: the GEMM that read xbuf[i] has finished
+        for i, (name, K, N, M, ar) in enumerate(plan):
+            wq, ws = weights[name]
+            b = i & 1
+            with torch.cuda.stream(s_in):
+                if done[b] is not None:
+                    s_in.wait_event(done[b])
+                x = xbuf[b][: M * K].view(M, K)
+                x.copy_(hx[K][:M], non_blocking=True)
+                up = torch.cuda.Event()
+                up.record(s_in)
+            with torch.cuda.stream(side):
+                side.wait_event(up)
+                xq, xs = kernel.act_quant(x)
+                y = kernel.fp8_gemm(xq, xs, wq, ws)
+                if ar:
+                    dist.all_reduce(y)
+                done[b] = torch.cuda.Event()
+                done[b].record(side)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(done[b])
+                hy[: M * N].view(M, N).copy_(y, non_blocking=True)
+                y.record_stream(s_out)
+        side.wait_stream(s_out)
+        side.wait_stream(s_in)
+
+    with torch.cuda.stream(side):
+        e2e_step()
     barrier()
     s0 = torch.cuda.Event(enable_timing=True); s1 = torch.cuda.Event(enable_timing=True)
-    s0.record()
-    for _ in range(args.steps):
-        e2e_step()
-    s1.record()
+    with torch.cuda.stream(side):
+        s0.record()
+        for _ in range(args.steps):
+            e2e_step()
+        s1.record()
     barrier()
     ms_e2e = s0.elapsed_time(s1)
     if world > 1:
@@ -390,10 +423,20 @@ def run_ours(args):
             elif M <= 64:
                 small_t += dt; small_b += by; n_small += len(rows)
     fp8_peak = 2.0 * peaks["bf16_tflops_sustained"]
+    # DRAM traffic per launch: ncu's dram__bytes_read.sum + dram__bytes_write.sum of one captured launch
+    # (bench.py --single, summaries under profiles/) divided by that problem's algorithmic bytes, applied
+    # to the average algorithmic bytes of the launches timed here (traffic tracks the operand and result
+    # sizes: each is moved once).
+    big_b = sum(gemm_bytes(M, N, K) for M in MS if M >= 256 for _, K, N, *_r in rows) / max(1, n_big // max(1, len(col_events)))
+    small_avg = sum(gemm_bytes(M, N, K) for M in MS if M <= 64 for _, K, N, *_r in rows) / max(1, n_small // max(1, len(col_events)))
+    ratio_big = NCU_TRAFFIC["token_major"][0] / gemm_bytes(*NCU_TRAFFIC["token_major"][1])
+    ratio_small = NCU_TRAFFIC["weight_major"][0] / gemm_bytes(*NCU_TRAFFIC["weight_major"][1])
     roofline = {
         "kernel": "fp8_gemm_tc_kernel<128,false> (tcgen05, token-major tiles; launches with M >= 256)",
         "bound": "tensor", "achieved": big_f / big_t / 1e12 if big_t else None, "peak": fp8_peak, "unit": "TFLOP/s",
-        "frac": (big_f / big_t / 1e12) / fp8_peak if big_t else None, "traffic": None,
+        "frac": (big_f / big_t / 1e12) / fp8_peak if big_t else None,
+        "traffic": ratio_big * big_b if n_big else None, "traffic_unit": "bytes per launch (average launch)",
+        "traffic_source": f"{NCU_TRAFFIC['token_major'][2]}: measured / algorithmic bytes = {ratio_big:.2f}",
         "peak_source": f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({peaks['source']}); FP8 issues at twice the bf16 rate",
         "launches": n_big, "avg_launch_us": big_t / n_big * 1e6 if n_big else None,
         "algorithmic": "2*M*N*K flops per launch",
@@ -401,7 +444,9 @@ def run_ours(args):
     roofline_decode = {
         "kernel": "fp8_gemm_tc_kernel<BN,true> (tcgen05, weight-major tiles, split-K; launches with M <= 64)",
         "bound": "hbm", "achieved": small_b / small_t / 1e9 if small_t else None, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-        "frac": (small_b / small_t / 1e9) / peaks["hbm_gbs"] if small_t else None, "traffic": None,
+        "frac": (small_b / small_t / 1e9) / peaks["hbm_gbs"] if small_t else None,
+        "traffic": ratio_small * small_avg if n_small else None, "traffic_unit": "bytes per launch (average launch)",
+        "traffic_source": f"{NCU_TRAFFIC['weight_major'][2]}: measured / algorithmic bytes = {ratio_small:.2f}",
         "peak_source": f"hbm_gbs of MEASURED_PEAKS.json ({peaks['source']})",
         "launches": n_small, "algorithmic": "M*K + N*K + scales + 2*M*N bytes per launch",
     }
@@ -446,7 +491,7 @@ def run_ours(args):
         "e2e": {"value": agg_e2e, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": ms_e2e / args.steps,
                 "path": "pinned host bf16 activations -> kernel.act_quant -> kernel.fp8_gemm -> bf16 result to pinned host; "
-                        "weights resident on the device"},
+                        "weights resident on the device; upload, compute and download on three streams"},
         "gpu_launches": len(plan) * args.steps, "gpu_launches_e2e": 2 * len(plan) * args.steps,
         "clocks": clocks, "per_column": detail,
     }
