@@ -201,6 +201,12 @@ def run_reference(args):
     if rank != 0:
         return
     from oracle import oracle as O
+    # torch.distributed.run exports OMP_NUM_THREADS=1 to its ranks; the reference arm is meant to use
+    # every host core this process may run on
+    try:
+        O.set_num_threads(len(os.sched_getaffinity(0)))
+    except AttributeError:
+        O.set_num_threads(os.cpu_count() or 1)
     rows = sweep_rows(1)
     M = 64
     cases = cpu_sample_inputs(rows, M)
@@ -261,6 +267,8 @@ def run_ours(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"   # the version banner goes to stdout, which carries the JSON line
         dist.init_process_group("nccl", device_id=dev)
     torch.set_default_dtype(torch.bfloat16)
     torch.manual_seed(1234 + rank)
@@ -605,6 +613,8 @@ def run_moe_layer(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"   # the version banner goes to stdout, which carries the JSON line
         dist.init_process_group("nccl", device_id=dev)
     torch.set_default_dtype(torch.bfloat16)
     dim, inter, E, topk, n_groups, topk_groups, route_scale = 7168, 2048, args.moe_experts, 8, 8, 4, 2.5
