@@ -61,7 +61,8 @@ SMALL = [  # (M, N, K, seed)
     (3, 192, 256, 1),
     (17, 64, 128, 21),
     (8, 256, 192, 22),       # K tail (K % 128 = 64)
-    (33, 200, 384, 23),      # N not a multiple of 8
+    (33, 200, 384, 23),      # N not a multiple of the tile width
+    (140, 204, 256, 29),     # N not a multiple of 8: the result cannot leave through a tensor map
     (64, 7168, 2048, 4),     # expert w2 at M = 64
     (100, 576, 512, 24),     # partial tiles in both directions
     (129, 130, 256, 25),
@@ -105,6 +106,59 @@ def test_fp8_gemm_is_deterministic_with_split_k(K):
     a = run(K, TC_WEIGHT, 4, xq, xs, wq, ws)
     b = run(K, TC_WEIGHT, 4, xq, xs, wq, ws)
     assert np.array_equal(bf16_bits(a), bf16_bits(b))
+
+
+def test_fp8_gemm_is_deterministic_with_split_k_token_major(K):
+    xq, xs, wq, ws = quantised_case(256, 512, 4096, 30)
+    ref = O.fp8_gemm(xq, xs, wq, ws)
+    a = run(K, TC_TOKEN, 4, xq, xs, wq, ws)
+    b = run(K, TC_TOKEN, 4, xq, xs, wq, ws)
+    assert np.array_equal(bf16_bits(a), bf16_bits(b))
+    assert_gemm_close(a, ref)
+
+
+def test_dependent_launch_chain_in_a_cuda_graph(K):
+    """weight_quant -> act_quant -> fp8_gemm -> act_quant -> fp8_gemm without any host synchronisation, eagerly
+    and as a replayed CUDA graph: the kernels are launched with programmatic stream serialisation, so each one
+    may start while its predecessor is still running and has to wait for it before touching its data."""
+    import dsv3_b200
+    g = torch.Generator(device="cpu").manual_seed(31)
+    x = torch.randn(96, 1024, generator=g).to(torch.bfloat16).cuda()
+    w1 = (torch.randn(2048, 1024, generator=g) * 0.02).to(torch.bfloat16).cuda()
+    w2 = (torch.randn(512, 2048, generator=g) * 0.02).to(torch.bfloat16).cuda()
+
+    def chain():
+        q1, s1 = dsv3_b200.weight_quant(w1)          # the weights themselves are produced just before use
+        q2, s2 = dsv3_b200.weight_quant(w2)
+        xq, xs = K.act_quant(x)
+        h = K.fp8_gemm(xq, xs, q1, s1)
+        hq, hs = K.act_quant(h)
+        return K.fp8_gemm(hq, hs, q2, s2)
+
+    # reference: the same chain with a device synchronisation after every call
+    torch.cuda.synchronize()
+    q1, s1 = dsv3_b200.weight_quant(w1); torch.cuda.synchronize()
+    q2, s2 = dsv3_b200.weight_quant(w2); torch.cuda.synchronize()
+    xq, xs = K.act_quant(x); torch.cuda.synchronize()
+    h = K.fp8_gemm(xq, xs, q1, s1); torch.cuda.synchronize()
+    hq, hs = K.act_quant(h); torch.cuda.synchronize()
+    want = K.fp8_gemm(hq, hs, q2, s2); torch.cuda.synchronize()
+    assert_gemm_close(want, O.fp8_gemm(hq.cpu(), hs.cpu(), q2.cpu(), s2.cpu()))
+
+    for _ in range(3):
+        assert torch.equal(chain(), want)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        chain()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            got = chain()
+        for _ in range(3):
+            got.zero_()
+            graph.replay()
+            side.synchronize()
+            assert torch.equal(got, want)
+    dsv3_b200.check_device_status()
 
 
 def test_fp8_gemm_matches_gpu_reference_goldens(K, golden_gpu):
