@@ -48,6 +48,25 @@ cudaError_t launch_dependent(void (*kern)(KArgs...), dim3 grid, dim3 block, size
 // current device (nullptr, with the error recorded, if it cannot be resolved).
 unsigned int* status_device_ptr();
 
+// Division of a 32-bit index by a run-time constant d >= 1: n / d == (umulhi(n, magic) + n) >> shift for every
+// 32-bit n (round-up method; the intermediate sum needs 33 bits, hence the 64-bit add).  An integer division
+// in device code costs several dozen instructions; the work-item decoders run one per tile per role.
+struct FastDiv {
+    uint32_t magic, shift, d;
+};
+inline FastDiv make_fast_div(uint32_t d) {
+    FastDiv f;
+    f.d = d;
+    uint32_t sh = 0;
+    while ((1ull << sh) < d) ++sh;
+    f.shift = sh;
+    f.magic = static_cast<uint32_t>(((1ull << 32) * ((1ull << sh) - d)) / d + 1);
+    return f;
+}
+__device__ __forceinline__ uint32_t fast_div(uint32_t n, const FastDiv& f) {
+    return static_cast<uint32_t>((static_cast<uint64_t>(__umulhi(n, f.magic)) + n) >> f.shift);
+}
+
 // ---------------------------------------------------------------- numerics
 // Approximate full-range division, the instruction Triton emits for `/` on fp32.
 __device__ __forceinline__ float div_full(float a, float b) {

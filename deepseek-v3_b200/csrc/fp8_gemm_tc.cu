@@ -74,6 +74,7 @@ struct TcParams {
     int kc;                 // number of K chunks
     int tiles_p, tiles_q;
     int splits;
+    FastDiv div_splits, div_per_group, div_raster, div_tiles_p;   // for the work-item decoder
     int raster;             // token-major tiles: P tiles (token tiles) that share consecutive Q tiles in the work order
     int tma_store;          // token-major tiles: results leave through shared memory and a TMA store (needs N % 8 == 0)
     int num_items;          // tiles_p * tiles_q * splits
@@ -87,7 +88,7 @@ struct TcParams {
 };
 
 // K chunks of one weight-major work item whose scales fit the shared-memory table: 144 (K <= 18432) for
-// 16- and 32-token tiles, 72 for 64-token tiles (the same 18 KB, which leaves room for eight 24 KB stages;
+// 16- and 32-token tiles, 72 for 64-token tiles (the same 18 KB, which leaves room for four 48 KB stages;
 // longer K is split, or uses the 32-token variant in grouped mode)
 constexpr int scale_tab_chunks(int bn) { return bn >= 64 ? 72 : 144; }
 
@@ -96,10 +97,12 @@ struct Cfg {
     // The pipeline moves "units" of kUC consecutive K chunks: one smem stage, one TMEM stage and one
     // round of hand-offs per unit.  Token-major tiles pair two chunks so that every hand-off (each costs
     // several hundred cycles of latency) covers twice the tensor-core work.
-    static constexpr int kUC = kSwap ? 1 : 2;
+    static constexpr int kUC = (kSwap && BN < 64) ? 1 : 2;
     static constexpr int kChunkBytes = kPRows * kChunk + BN * kChunk;      // P and Q tile of one chunk
     static constexpr int kStageBytes = kUC * kChunkBytes;
-    static constexpr int kTmemUnits = kTmemStages / kUC;                    // unit products resident in TMEM
+    // chunk products resident in TMEM: four 128-column accumulators, or eight of 64 columns
+    static constexpr int kAccs = (kSwap && BN == 64) ? 8 : kTmemStages;
+    static constexpr int kTmemUnits = kAccs / kUC;                          // unit products resident in TMEM
     // weight-major tiles: a_s * b_s of the item's chunks for the tile's BN tokens, [chunk][token]
     static constexpr int kScaleTabBytes = kSwap ? scale_tab_chunks(BN) * BN * 4 : 0;
     static constexpr int kGroupTabBytes = kSwap ? 2048 : 0;   // grouped mode: token-tile prefix per group
@@ -111,7 +114,7 @@ struct Cfg {
     // weight-major tiles: an even stage count, so that a stage always belongs to the same MMA issuer and
     // the issuer may probe its next full[] barrier (see the issuer loop)
     static constexpr int kStages = kSwap ? (kStagesCap & ~1) : kStagesCap;
-    static constexpr int kTmemCols = kTmemStages * BN;  // 64..512, a power of two
+    static constexpr int kTmemCols = kAccs * BN;  // 64..512, a power of two
     // tiles + result staging + tables + barriers + control words + slack for the 1024-byte alignment of the tiles
     static constexpr int kSmemBytes =
         kStages * kStageBytes + kStoreBytes + kScaleTabBytes + kGroupTabBytes + 1024 + 1024;
@@ -177,8 +180,8 @@ __device__ __forceinline__ Item decode_item(int item, const TcParams& p, const i
     Item it;
     if (kSwap && p.n_groups > 0) {
         // item -> (weight tile p_idx, token-tile slot); slot -> (group, tile within the group) by binary search
-        it.p_idx = item % p.tiles_p;
-        const int slot = item / p.tiles_p;
+        const int slot = static_cast<int>(fast_div(static_cast<uint32_t>(item), p.div_tiles_p));
+        it.p_idx = item - slot * p.tiles_p;
         it.tile = item;
         it.split = 0;
         it.q_idx = 0;
@@ -201,19 +204,20 @@ __device__ __forceinline__ Item decode_item(int item, const TcParams& p, const i
         return it;
     }
     it.group = 0;
-    it.tile = item / p.splits;
+    it.tile = static_cast<int>(fast_div(static_cast<uint32_t>(item), p.div_splits));
     it.split = item - it.tile * p.splits;
-    // grouped raster: 8 P-tiles share consecutive Q-tiles so a wave re-uses both operands in L2
+    // work order: `raster` P tiles share consecutive Q tiles so that a wave re-uses both operands in L2
     const int kGroup = p.raster;
     const int per_group = kGroup * p.tiles_q;
-    const int grp = it.tile / per_group;
+    const int grp = static_cast<int>(fast_div(static_cast<uint32_t>(it.tile), p.div_per_group));
     const int first_p = grp * kGroup;
     const int gsz = min(kGroup, p.tiles_p - first_p);
     const int r = it.tile - grp * per_group;
-    it.p_idx = first_p + r % gsz;
-    it.q_idx = r / gsz;
-    it.c0 = static_cast<int>((static_cast<int64_t>(p.kc) * it.split) / p.splits);
-    it.c1 = static_cast<int>((static_cast<int64_t>(p.kc) * (it.split + 1)) / p.splits);
+    it.q_idx = (gsz == kGroup) ? static_cast<int>(fast_div(static_cast<uint32_t>(r), p.div_raster)) : r / gsz;   // the last group may be shorter
+    it.p_idx = first_p + (r - it.q_idx * gsz);
+    // kc * split < 2^31 (kc < 2^24, at most 64 splits)
+    it.c0 = static_cast<int>(fast_div(static_cast<uint32_t>(p.kc * it.split), p.div_splits));
+    it.c1 = static_cast<int>(fast_div(static_cast<uint32_t>(p.kc * (it.split + 1)), p.div_splits));
     it.row0 = it.q_idx * BN;
     it.row_end = static_cast<int>(p.M);
     return it;
@@ -431,7 +435,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
         constexpr int SPC = CPT / HC;
         uint32_t probe = 0;   // result of test_wait on tfull[] for the next unit
         // token-major tiles: two read-back buffers of one chunk (64 columns) each
-        constexpr bool kBatched = (UC == 2);
+        constexpr bool kBatched = !kSwap;
         uint32_t va64[kBatched ? 64 : 1], vb64[kBatched ? 64 : 1];
         // Issues (does not wait for) the load of step `st` of chunk `j` of unit `gu`; the first step of a
         // unit first waits for the unit's products to be complete in TMEM.
@@ -544,7 +548,8 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
             } else {
                 if (n_mine > 0) ok = issue_load(unit_g(0), 0, 0, va);
             }
-            if constexpr (UC == 2) {
+            if constexpr (!kSwap) {
+                static_assert(UC == 2, "token-major tiles pair two chunks per unit");
                 // ---- token-major tiles: a thread reads its 64 columns of both
                 // chunks of the unit in one batch (tcgen05.wait::ld has no per-load granularity, so one wait
                 // per unit exposes the TMEM latency once), returns the TMEM stage at once and only then does
@@ -595,18 +600,23 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
                     sa1 = sb1;
                 }
             } else {
-                // ---- weight-major tiles: a unit is one chunk; one trip covers max(2, SPC) steps
+                // ---- weight-major tiles: a unit is one chunk (16- and 32-token tiles) or two (64-token tiles);
+                // a chunk is read back in SPC steps, one trip covers max(2, SPC) steps
                 constexpr int U = SPC > 2 ? SPC : 2;
-                const int n_steps = n_mine * SPC;
+                const int n_steps = n_ch * SPC;
                 auto step = [&](int t, auto u_c, uint32_t* cur, uint32_t* nxt) {
                     constexpr int u = decltype(u_c)::value;
                     constexpr int st = u % SPC;
                     const int T = t + u;
                     if (!ok || T >= n_steps) return;
-                    const int mu = T / SPC;
-                    finish_load(unit_g(mu), st == SPC - 1);
-                    if (T + 1 < n_steps) ok = issue_load(unit_g((T + 1) / SPC), 0, (u + 1) % SPC, nxt);
-                    fold(unit_k(mu), cur, 0.0f, std::integral_constant<int, st * (HC / 2)>{});
+                    const int c = T / SPC;                              // chunk of the item
+                    const bool last_of_unit = (st == SPC - 1) && ((c % UC) == UC - 1 || c == n_ch - 1);
+                    finish_load(unit_g(c / UC), last_of_unit);
+                    if (T + 1 < n_steps) {
+                        const int cn = (T + 1) / SPC;
+                        ok = issue_load(unit_g(cn / UC), cn % UC, (u + 1) % SPC, nxt);
+                    }
+                    fold(it.c0 + c, cur, 0.0f, std::integral_constant<int, st * (HC / 2)>{});
                 };
                 for (int t = 0; ok && t < n_steps; t += U) {
                     step(t, std::integral_constant<int, 0>{}, va, vb);
@@ -964,6 +974,10 @@ int launch_fp8_gemm_tc(const void* a, const float* a_s, const void* b, const flo
         const int64_t fit = (32ll << 20) / (static_cast<int64_t>(kPRows) * K);
         prm.raster = static_cast<int>(fit < 8 ? 8 : (fit > 64 ? 64 : fit));
     }
+    prm.div_splits = make_fast_div(static_cast<uint32_t>(prm.splits));
+    prm.div_raster = make_fast_div(static_cast<uint32_t>(prm.raster));
+    prm.div_per_group = make_fast_div(static_cast<uint32_t>(prm.raster) * static_cast<uint32_t>(prm.tiles_q));
+    prm.div_tiles_p = make_fast_div(static_cast<uint32_t>(prm.tiles_p));
     prm.num_items = pl.tiles_p * pl.tiles_q * pl.splits;
     prm.g_tmaps = nullptr;
     prm.g_bs = nullptr;
@@ -1057,6 +1071,10 @@ int launch_fp8_gemm_grouped(const void* table_dev, int n, const void* a, const f
     prm.splits = 1;
     prm.raster = 8;
     prm.tma_store = 0;
+    prm.div_splits = make_fast_div(1);
+    prm.div_raster = make_fast_div(8);
+    prm.div_per_group = make_fast_div(8);
+    prm.div_tiles_p = make_fast_div(static_cast<uint32_t>(prm.tiles_p));
     prm.g_tmaps = static_cast<const CUtensorMap*>(table_dev);
     prm.g_bs = reinterpret_cast<const float* const*>(static_cast<const uint8_t*>(table_dev) +
                                                      static_cast<size_t>(n) * sizeof(CUtensorMap));

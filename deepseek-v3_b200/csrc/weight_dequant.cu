@@ -24,15 +24,6 @@ __device__ __forceinline__ uint4 dequant8(uint32_t lo, uint32_t hi, float s) {
                       pack_bf16x2(__fmul_rn(c.x, s), __fmul_rn(c.y, s)), pack_bf16x2(__fmul_rn(d.x, s), __fmul_rn(d.y, s)));
 }
 
-// Division of a 32-bit index by a run-time constant: n / d == (umulhi(n, magic) + n) >> shift
-// (round-up method; the intermediate sum needs 33 bits, hence the 64-bit add).
-struct FastDiv {
-    uint32_t magic, shift, d;
-};
-__device__ __forceinline__ uint32_t fast_div(uint32_t n, const FastDiv& f) {
-    return static_cast<uint32_t>((static_cast<uint64_t>(__umulhi(n, f.magic)) + n) >> f.shift);
-}
-
 constexpr int kVecUnroll = 4;   // independent 8-byte loads in flight per thread
 
 // K % 8 == 0 and a power-of-two block size >= 8: an 8-element group never straddles a scale block.
@@ -122,12 +113,7 @@ int launch_weight_dequant(const void* w, const float* s, int64_t N, int64_t K, i
     if (vec) {
         const int64_t per_cta = static_cast<int64_t>(kThreads) * kVecUnroll;
         const int64_t grid = (total + per_cta - 1) / per_cta;
-        FastDiv fd;
-        fd.d = static_cast<uint32_t>(K >> 3);
-        uint32_t sh = 0;
-        while ((1ull << sh) < fd.d) ++sh;
-        fd.shift = sh;
-        fd.magic = static_cast<uint32_t>(((1ull << 32) * ((1ull << sh) - fd.d)) / fd.d + 1);
+        const FastDiv fd = make_fast_div(static_cast<uint32_t>(K >> 3));
         uint32_t bshift = 0;
         while ((1 << bshift) < block) ++bshift;
         weight_dequant_vec_kernel<<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
