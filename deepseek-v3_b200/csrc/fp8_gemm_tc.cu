@@ -886,7 +886,7 @@ TcPlan tc_plan(int64_t M, int64_t N, int64_t K, int force_kernel, int force_spli
         // bandwidth.  The factor with the lowest estimate wins (ties: fewer splits).
         const int sms = num_sms();
         const double c = pl.swap ? (pl.bn == 64 ? 0.30 : 0.22) : 0.26;
-        const double e0 = pl.swap ? 1.0 : 2.3, e1 = pl.swap ? 0.2 * pl.bn / 64.0 : 0.5;
+        const double e0 = pl.swap ? 2.2 : 2.3, e1 = pl.swap ? 0.2 * pl.bn / 64.0 : 0.5;
         const double hbm_floor = (static_cast<double>(N) * K + static_cast<double>(M) * K) / 6.0e6;
         double best = 1e30;
         for (int sfac = 1; sfac <= 8 && sfac <= pl.kc; ++sfac) {
