@@ -82,7 +82,16 @@ int dsv3_fp8_gemm_static(const void* a, const float* a_s, const void* b, const f
         return DSV3_ERR_UNSUPPORTED;
     }
     const int forced = gemm_policy_kernel();
-    const TcPlan pl = tc_plan(M, N, K, forced == 1 ? 0 : forced, gemm_policy_split());
+    TcPlan pl = tc_plan(M, N, K, forced == 1 ? 0 : forced, gemm_policy_split());
+    // The automatic plan may want more partial tiles than the array holds: fall back to fewer K splits of the
+    // same tile shape (a pinned split factor is honoured or refused, never changed).
+    if (gemm_policy_split() == 0) {
+        const int kernel = pl.swap ? 3 : 2;
+        for (int sfac = pl.splits - 1; sfac >= 1 && tc_workspace_bytes(pl, M, N) > kStaticScratchBytes; --sfac) {
+            const TcPlan alt = tc_plan(M, N, K, kernel, sfac);
+            if (alt.swap == pl.swap && alt.splits <= sfac) pl = alt;
+        }
+    }
     const size_t need = tc_workspace_bytes(pl, M, N);
     if (need > kStaticScratchBytes) {
         set_last_error("fp8_gemm_static: this problem (M=%lld N=%lld K=%lld, split-K %d) needs %zu bytes of scratch, "

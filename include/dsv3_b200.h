@@ -90,8 +90,10 @@ int dsv3_fp8_gemm(const void* a, const float* a_s, const void* b, const float* b
  * memory to its own arena at start-up (an allocation in the request path would fail, or would stall all
  * streams while the driver synchronises), and for C programs with no framework allocator to borrow from.
  *   - Every GPU that loads the library carries the array until the process exits.
- *   - Problems whose split-K plan needs more scratch than that are refused with DSV3_ERR_WORKSPACE;
- *     shapes the tcgen05 kernels cannot take (K % 16 != 0, unaligned pointers) with DSV3_ERR_UNSUPPORTED.
+ *   - When the automatic split-K plan needs more scratch than that, the call uses the largest split factor
+ *     that fits (down to none); a split factor pinned with dsv3_set_gemm_policy that does not fit is refused
+ *     with DSV3_ERR_WORKSPACE.  Shapes the tcgen05 kernels cannot take (K % 16 != 0, unaligned pointers)
+ *     are refused with DSV3_ERR_UNSUPPORTED.
  *   - The first call on a device looks up the array's device address (that device must be current); make
  *     that first call before starting any stream capture.
  *   - All calls on a device share the array: calls that can overlap on the GPU race on it.  The part that

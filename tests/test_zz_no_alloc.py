@@ -84,6 +84,20 @@ def test_static_scratch_gemm_matches_regular_entry_point_twice_in_a_row():
     assert lib.dsv3_check_device_status(stream, ctypes.byref(detail)) == _lib.OK
 
 
+def test_static_scratch_gemm_uses_fewer_splits_when_the_automatic_plan_does_not_fit():
+    from dsv3_b200 import _lib
+    lib = _lib.lib
+    _lib.check(lib.dsv3_set_gemm_policy(0, 0))
+    M, N, K = 384, 3072, 7168        # 72 tiles of 128 x 128: the automatic plan splits K in two, 9.4 MB of partial tiles
+    xq, xs, wq, ws = _quantised(M, N, K, 55)
+    ref, need = _regular(lib, _lib, xq, xs, wq, ws, M, N, K)
+    if need <= lib.dsv3_fp8_gemm_static_scratch_bytes():
+        pytest.skip("the automatic plan of this problem fits the array on this device")
+    out = _static(lib, _lib, xq, xs, wq, ws, M, N, K)
+    assert_gemm_close(out, ref.cpu())
+    assert_gemm_close(out, O.fp8_gemm(xq.cpu(), xs.cpu(), wq.cpu(), ws.cpu()))
+
+
 def test_static_scratch_gemm_refuses_what_does_not_fit():
     from dsv3_b200 import _lib
     lib = _lib.lib
