@@ -70,3 +70,21 @@ def test_tp_shards_on_two_gloo_ranks():
         assert ok_row, f"rank {rank}: row-parallel sum outside tolerance ({ratio_row:.3f})"
         assert ok_col, f"rank {rank}: column-parallel slice differs"
         assert ok_flops, f"rank {rank}: sharded flop count does not add up"
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_bench_shards_add_up_to_the_single_gpu_problem_set(world):
+    """bench.py --gpus N: the ranks' counted problems cover the single-GPU sweep exactly once (strong scaling),
+    every shard keeps K a multiple of the 128-wide quantisation block, and row-parallel shards all_reduce."""
+    sys.path.insert(0, ROOT)
+    import bench
+    ref = sum(bench.gemm_flops(m, n, k) for m in bench.MS for (_, k, n, *_r) in bench.sweep_rows(1))
+    total = 0
+    for rank in range(world):
+        rows = bench.sweep_rows(world, rank)
+        for name, k, n, _, all_reduce, counted in rows:
+            assert k % 128 == 0 and n > 0, (world, rank, name)
+            if all_reduce:
+                assert f"/tp{world}" in name, name
+        total += sum(bench.gemm_flops(m, n, k) for m in bench.MS for (_, k, n, _, _, c) in rows if c)
+    assert abs(total - ref) <= 1e-9 * ref
