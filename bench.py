@@ -264,11 +264,14 @@ def run_ours(args):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    # stdout carries the one JSON line and nothing else: whatever libraries print while the run lasts (NCCL's
+    # version banner, for one) is sent to stderr, and stdout is put back just before the line is printed
+    sys.stdout.flush()
+    saved_stdout = os.dup(1)
+    os.dup2(2, 1)
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
-            os.environ["NCCL_DEBUG"] = "WARN"   # the version banner goes to stdout, which carries the JSON line
         dist.init_process_group("nccl", device_id=dev)
     torch.set_default_dtype(torch.bfloat16)
     torch.manual_seed(1234 + rank)
@@ -503,7 +506,10 @@ def run_ours(args):
         "gpu_launches": len(plan) * args.steps, "gpu_launches_e2e": 2 * len(plan) * args.steps,
         "clocks": clocks, "per_column": detail,
     }
+    sys.stdout.flush()
+    os.dup2(saved_stdout, 1)
     print(json.dumps(line), flush=True)
+    os.dup2(2, 1)
     shutdown()
 
 
@@ -610,11 +616,14 @@ def run_moe_layer(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    # stdout carries the one JSON line and nothing else: whatever libraries print while the run lasts (NCCL's
+    # version banner, for one) is sent to stderr, and stdout is put back just before the line is printed
+    sys.stdout.flush()
+    saved_stdout = os.dup(1)
+    os.dup2(2, 1)
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
-            os.environ["NCCL_DEBUG"] = "WARN"   # the version banner goes to stdout, which carries the JSON line
         dist.init_process_group("nccl", device_id=dev)
     torch.set_default_dtype(torch.bfloat16)
     dim, inter, E, topk, n_groups, topk_groups, route_scale = 7168, 2048, args.moe_experts, 8, 8, 4, 2.5
