@@ -732,6 +732,8 @@ def run_moe_layer(args):
     ok = bool((err <= 2e-2 * (out_loop.float().abs() + rms)).all())
     flops = 2.0 * 3 * dim * inter * (T * topk + T)           # routed pairs + shared expert
     if rank == 0:
+        sys.stdout.flush()
+        os.dup2(saved_stdout, 1)
         print(json.dumps({
             "metric": "moe_layer_tokens_per_s", "value": T / (ms_grp * 1e-3), "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(2, args.warmup), "ms_per_step": ms_grp, "higher_is_better": True,
