@@ -50,6 +50,73 @@ __global__ void __launch_bounds__(kThreads) moe_combine_kernel(const __nv_bfloat
     }
 }
 
+// Bookkeeping of the expert loop in one launch (one CTA): groups the (token, expert) pairs by local expert and
+// orders every token's pairs by expert id.  Replaces `counts = bincount(indices)`, the per-expert
+// `where(indices == i)` (model.py:680-686) and the sort / scan / gather chain a framework needs for the same.
+//   seg [n + 1]        : seg[e] = first row of expert e in the grouped order, seg[n] = number of local pairs
+//   tok [P]            : token of the pair placed at each row (pairs of other ranks' experts follow seg[n])
+//   pair_row [P]       : scratch; row given to pair p, or -1 when its expert is not local
+//   pos_sorted, w_sorted [T, topk]: per token, rows and routing weights in ascending expert order
+// The order of an expert's rows is whatever the atomics give; every row's result depends on that row alone, so
+// the outputs do not depend on it.
+constexpr int kRouteThreads = 1024;
+constexpr int kRouteMaxExperts = 256;
+constexpr int kRouteMaxTopk = 32;
+
+__global__ void __launch_bounds__(kRouteThreads) moe_route_kernel(const int64_t* __restrict__ indices,
+                                                                  const float* __restrict__ weights, int64_t T, int topk,
+                                                                  int start, int n, int* __restrict__ seg,
+                                                                  int* __restrict__ tok, int* __restrict__ pair_row,
+                                                                  int* __restrict__ pos_sorted,
+                                                                  __nv_bfloat16* __restrict__ w_sorted) {
+    __shared__ int cnt[kRouteMaxExperts + 1];
+    __shared__ int cursor[kRouteMaxExperts + 1];
+    const int64_t P = T * topk;
+    for (int i = threadIdx.x; i <= n; i += kRouteThreads) cnt[i] = 0;
+    __syncthreads();
+    for (int64_t pr = threadIdx.x; pr < P; pr += kRouteThreads) {
+        const int64_t e = indices[pr] - start;
+        atomicAdd(&cnt[(e >= 0 && e < n) ? static_cast<int>(e) : n], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int i = 0; i <= n; ++i) {
+            cursor[i] = run;
+            if (i <= n) seg[i] = run;
+            run += cnt[i];
+        }
+    }
+    __syncthreads();
+    for (int64_t pr = threadIdx.x; pr < P; pr += kRouteThreads) {
+        const int64_t e = indices[pr] - start;
+        const bool local = (e >= 0 && e < n);
+        const int row = atomicAdd(&cursor[local ? static_cast<int>(e) : n], 1);
+        tok[row] = static_cast<int>(pr / topk);
+        pair_row[pr] = local ? row : -1;
+    }
+    __syncthreads();   // pair_row is read below by other threads of this CTA
+    for (int64_t t = threadIdx.x; t < T; t += kRouteThreads) {
+        int64_t e[kRouteMaxTopk];
+        int order[kRouteMaxTopk];
+        for (int j = 0; j < topk; ++j) {          // insertion sort of the token's experts, ascending
+            const int64_t ej = indices[t * topk + j];
+            int k = j;
+            while (k > 0 && e[k - 1] > ej) {
+                e[k] = e[k - 1];
+                order[k] = order[k - 1];
+                --k;
+            }
+            e[k] = ej;
+            order[k] = j;
+        }
+        for (int j = 0; j < topk; ++j) {
+            pos_sorted[t * topk + j] = pair_row[t * topk + order[j]];
+            w_sorted[t * topk + j] = __float2bfloat16_rn(weights[t * topk + order[j]]);
+        }
+    }
+}
+
 }  // namespace
 
 }  // namespace dsv3
@@ -81,6 +148,27 @@ int dsv3_fp8_gemm_grouped(const void* table, int n_groups, const void* a, const 
         return DSV3_ERR_INVALID_ARGUMENT;
     }
     return launch_fp8_gemm_grouped(table, n_groups, a, a_s, seg, rows_total, N, K, c, static_cast<cudaStream_t>(stream));
+}
+
+int dsv3_moe_route(const int64_t* indices, const float* weights, int64_t T, int topk, int start, int n_local,
+                   int32_t* seg, int32_t* tok, int32_t* pair_row, int32_t* pos_sorted, void* w_sorted,
+                   dsv3_stream_t stream) {
+    if (T < 0 || topk < 0 || n_local < 0) {
+        set_last_error("moe_route: negative size");
+        return DSV3_ERR_INVALID_ARGUMENT;
+    }
+    if (n_local > kRouteMaxExperts || topk > kRouteMaxTopk || T * topk >= (1ll << 31)) {
+        set_last_error("moe_route: at most %d local experts, top-%d and 2^31 pairs", kRouteMaxExperts, kRouteMaxTopk);
+        return DSV3_ERR_UNSUPPORTED;
+    }
+    if (!seg || (T * topk > 0 && (!indices || !weights || !tok || !pair_row || !pos_sorted || !w_sorted))) {
+        set_last_error("moe_route: null pointer");
+        return DSV3_ERR_INVALID_ARGUMENT;
+    }
+    moe_route_kernel<<<1, kRouteThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        indices, weights, T, topk, start, n_local, seg, tok, pair_row, pos_sorted, static_cast<__nv_bfloat16*>(w_sorted));
+    DSV3_CUDA_TRY(cudaGetLastError());
+    return DSV3_OK;
 }
 
 int dsv3_moe_combine(const void* o, const int32_t* pos, const void* w, int64_t T, int topk, int64_t dim, void* y,

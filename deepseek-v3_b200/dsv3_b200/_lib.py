@@ -24,7 +24,7 @@ EXPORTS = (
     "dsv3_version", "dsv3_strerror", "dsv3_last_error", "dsv3_act_quant", "dsv3_weight_dequant",
     "dsv3_fp8_gemm_workspace_bytes", "dsv3_fp8_gemm", "dsv3_set_gemm_policy", "dsv3_weight_quant",
     "dsv3_check_device_status", "dsv3_fp8_gemm_static", "dsv3_fp8_gemm_static_scratch_bytes",
-    "dsv3_group_table_bytes", "dsv3_group_table_build", "dsv3_fp8_gemm_grouped", "dsv3_moe_combine",
+    "dsv3_group_table_bytes", "dsv3_group_table_build", "dsv3_fp8_gemm_grouped", "dsv3_moe_combine", "dsv3_moe_route",
 )
 
 
@@ -61,6 +61,8 @@ def _load() -> ctypes.CDLL:
     lib.dsv3_fp8_gemm_grouped.restype = ci
     lib.dsv3_moe_combine.argtypes = [vp, vp, vp, i64, ci, i64, vp, vp]
     lib.dsv3_moe_combine.restype = ci
+    lib.dsv3_moe_route.argtypes = [vp, vp, i64, ci, ci, ci, vp, vp, vp, vp, vp, vp]
+    lib.dsv3_moe_route.restype = ci
     lib.dsv3_set_gemm_policy.argtypes = [ci, ci]
     lib.dsv3_weight_quant.argtypes = [vp, i64, i64, vp, vp, vp]
     lib.dsv3_check_device_status.argtypes = [vp, ctypes.POINTER(ctypes.c_uint32 * 4)]

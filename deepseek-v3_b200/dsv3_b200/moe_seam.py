@@ -4,7 +4,7 @@
 expert costs two host synchronisations (``bincount(...).tolist()``, ``torch.where``) and about six
 small launches.  ``grouped_moe_forward`` keeps inputs, outputs and arithmetic (same quantisation per
 token row, same bf16 rounding points, same ascending-expert accumulation order) but sorts the
-(token, expert) pairs on the device and runs each of the three projections as one grouped GEMM
+(token, expert) pairs on the device (one launch) and runs each of the three projections as one grouped GEMM
 over all local experts, followed by one combine kernel.  Nothing is read back to the host.
 
     import model, dsv3_b200
@@ -65,15 +65,18 @@ class GroupedExperts:
         P = T * topk
         n = self.n
         with torch.cuda.device(x.device):
-            # ---- sort the (token, expert) pairs by local expert id; pairs of other ranks' experts go last
-            key = indices.reshape(-1) - self.start
-            local = (key >= 0) & (key < n)
-            key = torch.where(local, key, torch.full_like(key, n))
-            order = torch.argsort(key, stable=True)
-            counts = torch.bincount(key, minlength=n + 1)
-            seg = torch.zeros(n + 1, dtype=torch.int32, device=x.device)
-            seg[1:] = torch.cumsum(counts[:n], 0).to(torch.int32)
-            tok = torch.div(order, topk, rounding_mode="floor")
+            # ---- group the (token, expert) pairs by local expert (pairs of other ranks' experts go last) and
+            # order every token's pairs by expert id: one launch, nothing read back
+            idx = indices if indices.dtype == torch.int64 else indices.long()
+            idx = idx if idx.is_contiguous() else idx.contiguous()
+            wf = (weights if weights.dtype == torch.float32 else weights.float()).contiguous()
+            seg = torch.empty(n + 1, dtype=torch.int32, device=x.device)
+            tok = torch.empty(P, dtype=torch.int32, device=x.device)
+            pair_row = torch.empty(P, dtype=torch.int32, device=x.device)
+            pos_s = torch.empty(T, topk, dtype=torch.int32, device=x.device)
+            w_s = torch.empty(T, topk, dtype=torch.bfloat16, device=x.device)
+            _lib.check(lib.dsv3_moe_route(idx.data_ptr(), wf.data_ptr(), T, topk, self.start, n, seg.data_ptr(),
+                                          tok.data_ptr(), pair_row.data_ptr(), pos_s.data_ptr(), w_s.data_ptr(), _stream()))
             # ---- quantise every token once, gather the rows in expert order
             xq, xs = _quantised(x, 128, self.scale_fmt)
             xq_p = xq.view(torch.uint8).index_select(0, tok).view(torch.float8_e4m3fn)
@@ -83,12 +86,6 @@ class GroupedExperts:
             hq, hs = act_quant(h, 128, self.scale_fmt)
             o = self.gemm("w2", hq, hs, seg)
             # ---- y[t] = sum over the token's local experts, ascending expert id, bf16 at every step
-            pos_flat = torch.empty(P, dtype=torch.int32, device=x.device)
-            pos_flat[order] = torch.arange(P, dtype=torch.int32, device=x.device)
-            pos = torch.where(local, pos_flat, torch.full_like(pos_flat, -1)).view(T, topk)
-            _, by_expert = indices.sort(dim=1)
-            pos_s = pos.gather(1, by_expert).contiguous()
-            w_s = weights.gather(1, by_expert).to(torch.bfloat16).contiguous()
             y = torch.empty(T, self.dim, dtype=torch.bfloat16, device=x.device)
             _lib.check(lib.dsv3_moe_combine(o.data_ptr(), pos_s.data_ptr(), w_s.data_ptr(), T, topk, self.dim,
                                             y.data_ptr(), _stream()))

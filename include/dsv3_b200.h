@@ -134,6 +134,23 @@ int dsv3_fp8_gemm_grouped(const void* table, int n_groups, const void* a, const 
                           int64_t rows_total, int64_t N, int64_t K, void* c, dsv3_stream_t stream);
 
 /*
+ * Routing bookkeeping of the expert loop in one launch -- replaces `counts = torch.bincount(indices.flatten())`
+ * and the per-expert `idx, top = torch.where(indices == i)` of model.py:680-686 (two host synchronisations per
+ * expert in the reference).  Groups the (token, expert) pairs by local expert and orders every token's pairs by
+ * expert id.  All arrays are device memory.
+ *   indices : int64 [T, topk] expert ids           weights : float [T, topk] routing weights
+ *   start, n_local : this rank owns experts [start, start + n_local), n_local <= 256, topk <= 32
+ *   seg  : int32 [n_local + 1] out; seg[e] = first row of expert e, seg[n_local] = number of local pairs
+ *   tok  : int32 [T*topk] out; token of the pair at each row (rows >= seg[n_local]: pairs of other ranks' experts)
+ *   pair_row : int32 [T*topk] scratch
+ *   pos_sorted : int32 [T, topk] out; w_sorted : bf16 [T, topk] out -- the `pos` and `w` of dsv3_moe_combine
+ * The order of the rows inside one expert is not specified; no result depends on it.
+ */
+int dsv3_moe_route(const int64_t* indices, const float* weights, int64_t T, int topk, int start, int n_local,
+                   int32_t* seg, int32_t* tok, int32_t* pair_row, int32_t* pos_sorted, void* w_sorted,
+                   dsv3_stream_t stream);
+
+/*
  * Scatter-add of the expert outputs -- the `y[idx] += expert(x[idx]) * weights[idx, top, None]` of
  * model.py:689 for all experts at once, with the same bf16 rounding (product, then every partial sum) and
  * the same ascending-expert order per token.

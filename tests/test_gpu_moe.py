@@ -142,3 +142,41 @@ def test_install_moe_rebinds_forward():
     assert isinstance(out, torch.Tensor) and out.shape == (6, 256)
     mod.gemm_impl = "bf16"
     assert moe.forward(x) == "original"
+
+
+@pytest.mark.parametrize("T,topk,E,start,n", [(64, 8, 256, 0, 256), (300, 6, 64, 16, 32), (1, 8, 256, 224, 32), (2048, 8, 256, 0, 256)])
+def test_moe_route_groups_pairs_by_expert_and_orders_each_tokens_pairs(T, topk, E, start, n):
+    """dsv3_moe_route against the torch operations it replaces (bincount / where / sort of model.py:680-686)."""
+    from dsv3_b200 import _lib
+    lib = _lib.lib
+    g = torch.Generator(device="cpu").manual_seed(T * 31 + topk)
+    scores = torch.rand(T, E, generator=g)
+    weights, indices = scores.topk(topk, dim=-1)            # distinct experts per token, descending score
+    indices, weights = indices.cuda(), weights.float().cuda()
+    P = T * topk
+    seg = torch.empty(n + 1, dtype=torch.int32, device="cuda")
+    tok = torch.empty(P, dtype=torch.int32, device="cuda")
+    pair_row = torch.empty(P, dtype=torch.int32, device="cuda")
+    pos_s = torch.empty(T, topk, dtype=torch.int32, device="cuda")
+    w_s = torch.empty(T, topk, dtype=torch.bfloat16, device="cuda")
+    _lib.check(lib.dsv3_moe_route(indices.data_ptr(), weights.data_ptr(), T, topk, start, n, seg.data_ptr(), tok.data_ptr(),
+                                  pair_row.data_ptr(), pos_s.data_ptr(), w_s.data_ptr(), torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    key = indices.reshape(-1) - start
+    local = (key >= 0) & (key < n)
+    counts = torch.bincount(torch.where(local, key, torch.full_like(key, n)), minlength=n + 1)
+    want_seg = torch.zeros(n + 1, dtype=torch.int64, device="cuda")
+    want_seg[1:] = torch.cumsum(counts[:n], 0)
+    assert torch.equal(seg.long(), want_seg)
+    # every pair got a distinct row; local pairs sit inside their expert's segment and carry their token
+    rows = torch.where(local, pair_row.long(), torch.full_like(key, -1))
+    lp = torch.nonzero(local).flatten()
+    assert torch.equal(torch.sort(rows[lp]).values, torch.arange(int(want_seg[n]), device="cuda"))
+    e = key[lp]
+    assert bool(((rows[lp] >= want_seg[e]) & (rows[lp] < want_seg[e + 1])).all())
+    assert torch.equal(tok.long()[rows[lp]], lp // topk)
+    assert torch.equal(torch.sort(tok.long()).values, torch.arange(P, device="cuda") // topk)
+    # per token: ascending expert order
+    _, by_expert = indices.sort(dim=1)
+    assert torch.equal(pos_s.long(), rows.view(T, topk).gather(1, by_expert))
+    assert torch.equal(w_s, weights.gather(1, by_expert).to(torch.bfloat16))
