@@ -662,10 +662,11 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
                 const int slot = static_cast<int>(item_no & 1u);
                 promo_barrier<kWriters>();
                 if (threadIdx.x == kFirstPromoWarp * 32) {
-                    __threadfence();
-                    const int t = atomicAdd(p.tickets + it.tile, 1);
+                    // one acquire-release atomic: releases the partial tiles (cumulative over the barrier above) and
+                    // acquires the other splits' tiles for the reads below
+                    int t;
+                    asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(t) : "l"(p.tickets + it.tile) : "memory");
                     if (t == p.splits - 1) p.tickets[it.tile] = 0;  // last arrival: leave the ticket clean
-                    __threadfence();                                 // acquire side for the reads below
                     ctl->ticket[slot] = t;
                 }
                 promo_barrier<kWriters>();
