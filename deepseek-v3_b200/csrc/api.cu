@@ -159,8 +159,8 @@ int dsv3_weight_quant(const void* w, int64_t N, int64_t K, void* q, float* s, ds
 }
 
 int dsv3_set_gemm_policy(int kernel, int split_k) {
-    if (kernel < 0 || kernel > 3 || split_k < 0 || split_k > 64) {
-        set_last_error("set_gemm_policy: kernel must be 0..3 and split_k 0..64");
+    if (kernel < 0 || kernel > 4 || split_k < 0 || split_k > 64) {
+        set_last_error("set_gemm_policy: kernel must be 0..4 and split_k 0..64");
         return DSV3_ERR_INVALID_ARGUMENT;
     }
     g_force_kernel = kernel;
@@ -171,6 +171,7 @@ int dsv3_set_gemm_policy(int kernel, int split_k) {
 size_t dsv3_fp8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K) {
     if (M <= 0 || N <= 0 || K <= 0 || g_force_kernel == 1 || (K % 16) != 0) return 0;
     const TcPlan pl = tc_plan(M, N, K, g_force_kernel, g_force_split);
+    if (pl.error != DSV3_OK) return 0;     // dsv3_fp8_gemm reports the reason
     return tc_workspace_bytes(pl, M, N);
 }
 
@@ -198,6 +199,7 @@ int dsv3_fp8_gemm(const void* a, const float* a_s, const void* b, const float* b
         return DSV3_ERR_UNSUPPORTED;
     }
     const TcPlan pl = tc_plan(M, N, K, g_force_kernel, g_force_split);
+    if (pl.error != DSV3_OK) return pl.error;
     return launch_fp8_gemm_tc(a, a_s, b, b_s, M, N, K, c, workspace, workspace_bytes, pl, st);
 }
 

@@ -266,6 +266,63 @@ __device__ __forceinline__ void tc_ld_x64(uint32_t taddr, uint32_t* r) {
         : "memory");
 }
 
+// ---------------------------------------------------------------- PTX: CTA pairs (cluster of two, tcgen05 cta_group::2)
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// shared::cluster address of the location `addr` (a shared::cta address of this CTA) in the CTA of rank `rank`
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+// Arrive on an mbarrier of any CTA of the cluster (shared::cluster address).  Default semantics (release at CTA
+// scope): a release at cluster scope makes every arrive wait for a cluster-wide fence (measured: the pair kernel
+// ran 2.3x slower with it), and what these arrives order is tensor memory, which the tcgen05 fences cover.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory");
+}
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+// 2-D tiled load global -> this CTA's shared memory whose completion is signalled on an mbarrier that may live
+// in the peer CTA of the pair (shared::cluster address).  No multicast: the data goes to one CTA.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* tmap, int x, int y, uint32_t bar_cluster) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(bar_cluster)
+        : "memory");
+}
+// Whole-warp, in both CTAs of a pair (same warp index, same slot offset): allocate `cols` TMEM columns in both.
+__device__ __forceinline__ void tc_alloc_pair(uint32_t slot_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tc_dealloc_pair(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+// One MMA over both SMs of a pair (issued by one thread of the even-ranked CTA): D rows 0..127 in this CTA's
+// TMEM, rows 128..255 in the peer's; each CTA supplies its own half of A (M) and of B (N) at the same
+// shared-memory offsets.
+__device__ __forceinline__ void tc_mma_f8_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                               uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrive on one mbarrier (shared::cluster address: this CTA's or the peer's) once all tcgen05 operations issued
+// so far by this thread are done.
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar_cluster) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster) : "memory");
+}
+
 // Shared-memory operand descriptor for a K-major tile whose rows are 128 bytes and
 // which was written by TMA with the 128-byte swizzle: 8-row groups are 1024 bytes
 // apart (stride byte offset), descriptor version 1, layout type 2 (SWIZZLE_128B).

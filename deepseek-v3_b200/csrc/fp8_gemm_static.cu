@@ -82,14 +82,23 @@ int dsv3_fp8_gemm_static(const void* a, const float* a_s, const void* b, const f
         return DSV3_ERR_UNSUPPORTED;
     }
     const int forced = gemm_policy_kernel();
-    TcPlan pl = tc_plan(M, N, K, forced == 1 ? 0 : forced, gemm_policy_split());
-    // The automatic plan may want more partial tiles than the array holds: fall back to fewer K splits of the
-    // same tile shape (a pinned split factor is honoured or refused, never changed).
-    if (gemm_policy_split() == 0) {
+    if (forced == 1) {
+        set_last_error("fp8_gemm_static: gemm policy 1 (CUDA-core kernel) is not offered here; it needs no scratch, "
+                       "call dsv3_fp8_gemm");
+        return DSV3_ERR_UNSUPPORTED;
+    }
+    TcPlan pl = tc_plan(M, N, K, forced, gemm_policy_split());
+    if (pl.error != DSV3_OK) return pl.error;
+    // The automatic plan may want more partial tiles than the array holds: fall back to the largest split factor
+    // of the same tile shape that fits (a pinned split factor is honoured or refused, never changed).
+    if (gemm_policy_split() == 0 && tc_workspace_bytes(pl, M, N) > kStaticScratchBytes) {
         const int kernel = pl.swap ? 3 : 2;
-        for (int sfac = pl.splits - 1; sfac >= 1 && tc_workspace_bytes(pl, M, N) > kStaticScratchBytes; --sfac) {
+        for (int sfac = pl.splits - 1; sfac >= 1; --sfac) {
             const TcPlan alt = tc_plan(M, N, K, kernel, sfac);
-            if (alt.swap == pl.swap && alt.splits <= sfac) pl = alt;
+            if (alt.error == DSV3_OK && tc_workspace_bytes(alt, M, N) <= kStaticScratchBytes) {
+                pl = alt;
+                break;
+            }
         }
     }
     const size_t need = tc_workspace_bytes(pl, M, N);

@@ -42,6 +42,7 @@
 
 #include "common.cuh"
 #include "gemm_plan.cuh"
+#include "tc_wait.cuh"
 
 namespace dsv3 {
 
@@ -57,10 +58,7 @@ constexpr int kRegsControl = 40;
 constexpr int kRegsPromo = 232;
 static_assert(128 * kRegsControl + 256 * kRegsPromo <= 384 * 168, "register pool");
 
-constexpr int kPRows = 128;               // MMA M
-constexpr int kChunk = 128;               // K elements (= bytes) per chunk
 constexpr int kTmemStages = 4;
-constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;
 constexpr int kMaxTickets = DSV3_WORKSPACE_HEADER_BYTES / 4;
 
 struct TcParams {
@@ -125,44 +123,6 @@ struct Cfg {
     // more than half of an SM's shared memory, so two CTAs can never share an SM (and its TMEM)
     static_assert(kSmemBytes > 116 * 1024, "one CTA per SM");
 };
-
-struct Control {
-    volatile uint32_t abort_flag;
-    uint32_t tmem_base;
-    volatile int ticket[2];
-};
-
-// Waits for the phase with the given parity.  The common case costs one or a few try_wait
-// instructions; the wall-clock budget is only consulted after a few thousand failed polls (reading
-// the global timer is slow enough to throttle the pipeline if it sat on the fast path).
-__device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, Control* ctl, unsigned int* status,
-                                             uint32_t what, uint32_t g) {
-    uint64_t t0 = 0;
-    for (uint32_t spins = 0;; ++spins) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if (spins >= 4096u && (spins & 255u) == 0u) {
-            if (ctl->abort_flag) return false;
-            const uint64_t now = global_timer_ns();
-            if (t0 == 0) {
-                t0 = now;
-            } else if (now - t0 > kWaitLimitNs) {
-                ctl->abort_flag = 1;
-                if (atomicCAS(&status[0], 0u, 1u) == 0u) {
-                    status[1] = what;        // 1 empty, 2 full, 3 tmem-empty, 4 tmem-full, 7-8 scale table
-                    status[2] = g;           // chunk counter of the waiting role
-                    status[3] = blockIdx.x;
-                }
-                return false;
-            }
-        }
-    }
-}
-
-// bounded_wait preceded by the result of an earlier probe of the same barrier and parity.
-__device__ __forceinline__ bool wait_probed(uint32_t probed, uint32_t bar, uint32_t parity, Control* ctl,
-                                            unsigned int* status, uint32_t what, uint32_t g) {
-    return probed != 0u || bounded_wait(bar, parity, ctl, status, what, g);
-}
 
 struct Item {
     int p_idx, q_idx, split, tile;
@@ -368,6 +328,10 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
                     }
                 }
             }
+            // Nothing waits for the commits onto the empty[] barriers of the last units; wait for them here so
+            // that none is in flight when the CTA leaves (it would land in whatever CTA gets this shared memory next).
+            for (uint32_t d = (g > static_cast<uint32_t>(NS) ? g - NS : 0u); ok && d < g; ++d)
+                ok = bounded_wait(empty_bar(d % NS), (d / NS) & 1u, ctl, p.status, 1, d);
         }
     } else if (warp <= kIssuers) {
         // ------------------------------------------------------------ MMA issuers (chunk g -> issuer g % kIssuers)
@@ -775,11 +739,13 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
 
 // -------------------------------------------------------------------- host side
 
+}  // namespace
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-EncodeTiledFn encode_fn() {
+static EncodeTiledFn encode_fn() {
     static EncodeTiledFn fn = nullptr;
     static std::once_flag once;
     std::call_once(once, [] {
@@ -836,6 +802,8 @@ int make_tmap_out(CUtensorMap* map, void* base, int64_t M, int64_t N) {
     return DSV3_OK;
 }
 
+namespace {
+
 template <int BN, bool kSwap>
 int launch_variant(const CUtensorMap& tp, const CUtensorMap& tq, const CUtensorMap& tc, const TcParams& prm,
                    cudaStream_t stream) {
@@ -860,10 +828,15 @@ bool tc_supported(const void* a, const void* b, const void* c, int64_t M, int64_
            (reinterpret_cast<uintptr_t>(b) % 16) == 0 && (reinterpret_cast<uintptr_t>(c) % 16) == 0 && M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31);
 }
 
+// Pinned values (dsv3_set_gemm_policy) are honoured or refused (pl.error), never rewritten; the automatic
+// plan adapts freely.
 TcPlan tc_plan(int64_t M, int64_t N, int64_t K, int force_kernel, int force_split) {
     TcPlan pl;
+    pl.error = DSV3_OK;
+    pl.pair = false;
+    pl.splits = 1;
     pl.kc = static_cast<int>((K + kChunk - 1) / kChunk);
-    pl.swap = (force_kernel == 3) || (force_kernel != 2 && M <= 64);
+    pl.swap = (force_kernel == 3) || (force_kernel == 0 && M <= 64);
     if (pl.swap) {
         pl.bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
         pl.tiles_p = static_cast<int>((N + kPRows - 1) / kPRows);
@@ -874,10 +847,28 @@ TcPlan tc_plan(int64_t M, int64_t N, int64_t K, int force_kernel, int force_spli
         pl.tiles_q = static_cast<int>((N + 127) / 128);
     }
     const int64_t tiles = static_cast<int64_t>(pl.tiles_p) * pl.tiles_q;
+    if (tiles * 64 >= (1ll << 31)) {     // the work-item counters are 32-bit (at most 64 splits)
+        set_last_error("fp8_gemm: %lld output tiles are more than the work-item counter holds", static_cast<long long>(tiles));
+        pl.error = DSV3_ERR_UNSUPPORTED;
+        return pl;
+    }
     int splits = 1;
     const int tab = pl.swap ? scale_tab_chunks(pl.bn) : (1 << 30);   // chunks per item the scale table holds
     if (force_split > 0) {
         splits = force_split;
+        const char* why = nullptr;
+        if (splits > pl.kc) why = "more splits than 128-wide K chunks";
+        else if (splits > 1 && tiles > kMaxTickets) why = "more output tiles than the workspace header has tickets";
+        else if ((pl.kc + splits - 1) / splits > tab) why = "K range per split exceeds the weight-major kernel's scale table";
+        else if (force_kernel == 4 && splits > 1) why = "the CTA-pair kernel does not split K";
+        if (why) {
+            set_last_error("fp8_gemm: pinned split factor %d cannot be used for M=%lld N=%lld K=%lld: %s", force_split,
+                           static_cast<long long>(M), static_cast<long long>(N), static_cast<long long>(K), why);
+            pl.error = DSV3_ERR_UNSUPPORTED;
+            return pl;
+        }
+    } else if (force_kernel == 4) {
+        splits = 1;
     } else if (tiles <= kMaxTickets) {
         // Splitting K fills idle SMs, but every split item pays for parking its partial tile, a fence and a
         // ticket, and the last arrival of a tile sums the partial tiles.  Estimate, fitted to B200
@@ -903,18 +894,25 @@ TcPlan tc_plan(int64_t M, int64_t N, int64_t K, int force_kernel, int force_spli
             }
         }
     }
-    if (splits > pl.kc) splits = pl.kc;
-    if (splits < 1) splits = 1;
-    if (tiles > kMaxTickets) splits = 1;
-    if ((pl.kc + splits - 1) / splits > tab) {
-        // the weight-major kernel keeps an item's scales in a shared-memory table
+    if (force_split == 0 && (pl.kc + splits - 1) / splits > tab) {
+        // the weight-major kernel keeps an item's scales in a shared-memory table: split K until an item fits
         splits = (pl.kc + tab - 1) / tab;
-        if (splits > 32 || tiles > kMaxTickets) {   // absurdly long K: use token-major tiles instead
-            TcPlan alt = tc_plan(M, N, K, 2, 1);
-            return alt;
+        if (splits > 32 || tiles > kMaxTickets) {
+            if (force_kernel == 3) {
+                set_last_error("fp8_gemm: K=%lld is too long for the weight-major kernel's scale table", static_cast<long long>(K));
+                pl.error = DSV3_ERR_UNSUPPORTED;
+                return pl;
+            }
+            return tc_plan(M, N, K, 2, 0);   // automatic choice, absurdly long K: token-major tiles instead
         }
     }
     pl.splits = splits;
+    if (force_kernel == 4 && !tm_pair_supported(M, N, K, true)) {
+        set_last_error("fp8_gemm: the CTA-pair kernel needs more than 128 tokens (M=%lld)", static_cast<long long>(M));
+        pl.error = DSV3_ERR_UNSUPPORTED;
+        return pl;
+    }
+    pl.pair = !pl.swap && splits == 1 && (force_kernel == 4 || (force_kernel == 0 && tm_pair_supported(M, N, K, false)));
     return pl;
 }
 
@@ -938,6 +936,8 @@ int launch_fp8_gemm_tc(const void* a, const float* a_s, const void* b, const flo
             return DSV3_ERR_WORKSPACE;
         }
     }
+    if (pl.error != DSV3_OK) return pl.error;
+    if (pl.pair) return launch_fp8_gemm_tm(a, a_s, b, b_s, M, N, K, c, stream);
     CUtensorMap tp, tq, tc;
     memset(&tc, 0, sizeof(tc));
     int rc;
@@ -979,7 +979,7 @@ int launch_fp8_gemm_tc(const void* a, const float* a_s, const void* b, const flo
     prm.div_raster = make_fast_div(static_cast<uint32_t>(prm.raster));
     prm.div_per_group = make_fast_div(static_cast<uint32_t>(prm.raster) * static_cast<uint32_t>(prm.tiles_q));
     prm.div_tiles_p = make_fast_div(static_cast<uint32_t>(prm.tiles_p));
-    prm.num_items = pl.tiles_p * pl.tiles_q * pl.splits;
+    prm.num_items = pl.tiles_p * pl.tiles_q * pl.splits;   // < 2^31: checked by tc_plan
     prm.g_tmaps = nullptr;
     prm.g_bs = nullptr;
     prm.g_seg = nullptr;

@@ -1,13 +1,17 @@
 // Internal interface of the tcgen05 fp8_gemm kernels: problem geometry ("plan") and launcher.
 #pragma once
 
+#include <cuda.h>
+
 #include "common.cuh"
 
 namespace dsv3 {
 
 // Geometry chosen for a problem; shared by the workspace query and the launch.
 struct TcPlan {
+    int error;  // DSV3_OK, or the status to return (detail recorded): a pinned kernel / split factor that cannot be honoured
     bool swap;  // true: weights on the MMA M axis (small M)
+    bool pair;  // token-major tiles on CTA pairs (fp8_gemm_tm.cu); never with split-K
     int bn;     // rows of the second operand tile
     int tiles_p, tiles_q, splits, kc;
 };
@@ -19,6 +23,18 @@ size_t tc_workspace_bytes(const TcPlan& pl, int64_t M, int64_t N);
 int launch_fp8_gemm_tc(const void* a, const float* a_s, const void* b, const float* b_s, int64_t M, int64_t N,
                        int64_t K, void* c, void* workspace, size_t workspace_bytes, const TcPlan& pl,
                        cudaStream_t stream);
+
+// Tensor maps over the operands as they lie in memory.  Operand: [rows, K] bytes, row-major; box = 128 bytes x
+// box_rows, 128-byte swizzle, zero fill outside.  Result: [M, N] bf16, row-major; box = 64 columns x 128 rows,
+// 128-byte swizzle (N % 8 == 0).
+int make_tmap(CUtensorMap* map, const void* base, int64_t rows, int64_t K, int box_rows);
+int make_tmap_out(CUtensorMap* map, void* base, int64_t M, int64_t N);
+
+// Token-major kernel on CTA pairs (256 x 128 tiles, tcgen05 cta_group::2, no split-K): fp8_gemm_tm.cu.
+// `forced`: the kernel was pinned, so only its hard limit applies, not the speed heuristic.
+bool tm_pair_supported(int64_t M, int64_t N, int64_t K, bool forced);
+int launch_fp8_gemm_tm(const void* a, const float* a_s, const void* b, const float* b_s, int64_t M, int64_t N,
+                       int64_t K, void* c, cudaStream_t stream);
 
 // Grouped GEMM over per-group weights (MoE experts).
 size_t group_table_bytes(int n);

@@ -15,7 +15,7 @@ import torch
 from . import _lib
 from ._lib import lib
 
-KERNEL_AUTO, KERNEL_CUDA_CORE, KERNEL_TC_TOKEN_MAJOR, KERNEL_TC_WEIGHT_MAJOR = 0, 1, 2, 3
+KERNEL_AUTO, KERNEL_CUDA_CORE, KERNEL_TC_TOKEN_MAJOR, KERNEL_TC_WEIGHT_MAJOR, KERNEL_TC_TOKEN_PAIR = 0, 1, 2, 3, 4
 
 _workspaces: Dict[Tuple[int, int], torch.Tensor] = {}
 

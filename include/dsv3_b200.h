@@ -93,7 +93,8 @@ int dsv3_fp8_gemm(const void* a, const float* a_s, const void* b, const float* b
  *   - When the automatic split-K plan needs more scratch than that, the call uses the largest split factor
  *     that fits (down to none); a split factor pinned with dsv3_set_gemm_policy that does not fit is refused
  *     with DSV3_ERR_WORKSPACE.  Shapes the tcgen05 kernels cannot take (K % 16 != 0, unaligned pointers)
- *     are refused with DSV3_ERR_UNSUPPORTED.
+ *     and gemm policy 1 (the CUDA-core kernel, which needs no scratch at all) are refused with
+ *     DSV3_ERR_UNSUPPORTED.
  *   - The first call on a device looks up the array's device address (that device must be current); make
  *     that first call before starting any stream capture.
  *   - All calls on a device share the array: calls that can overlap on the GPU race on it.  The part that
@@ -107,9 +108,13 @@ int dsv3_fp8_gemm_static(const void* a, const float* a_s, const void* b, const f
 /*
  * Kernel selection for fp8_gemm, for tests and benchmarks:
  *   0 = automatic (default), 1 = CUDA-core tiled kernel (any shape),
- *   2 = tcgen05 kernel, tokens on the MMA M axis, 3 = tcgen05 kernel, weights on the
- *   MMA M axis (small M).  Values 2 and 3 fail with DSV3_ERR_UNSUPPORTED on shapes
- *   those kernels cannot take.  split_k = 0 lets the library choose.
+ *   2 = tcgen05 kernel, tokens on the MMA M axis, one CTA per 128 x 128 tile,
+ *   3 = tcgen05 kernel, weights on the MMA M axis (small M),
+ *   4 = tcgen05 kernel, tokens on the MMA M axis, CTA pairs on 256 x 128 tiles (needs M > 128, no split-K).
+ * split_k = 0 lets the library choose.  A pinned kernel or split factor is honoured or the GEMM call fails
+ * with DSV3_ERR_UNSUPPORTED (shape the kernel cannot take, split factor that does not fit); it is never
+ * silently replaced.  The setting is one process-wide pair of integers read by every later dsv3_fp8_gemm /
+ * dsv3_fp8_gemm_static call of any thread; change it only while no other thread is inside the library.
  */
 int dsv3_set_gemm_policy(int kernel, int split_k);
 

@@ -62,7 +62,7 @@ def special_act_input():
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--device", choices=["cpu", "cuda"], default="cpu")
-    ap.add_argument("--reference-dir", default="/root/reference/inference")
+    ap.add_argument("--reference-dir", required=True, help="the reference's inference/ directory (read only)")
     ap.add_argument("--out", default=None)
     args = ap.parse_args()
 

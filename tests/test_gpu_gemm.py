@@ -15,7 +15,7 @@ from gpu_util import bf16_bits, assert_gemm_close
 
 pytestmark = pytest.mark.gpu
 
-AUTO, CORE, TC_TOKEN, TC_WEIGHT = 0, 1, 2, 3
+AUTO, CORE, TC_TOKEN, TC_WEIGHT, TC_PAIR = 0, 1, 2, 3, 4
 
 
 @pytest.fixture(scope="module")
@@ -70,16 +70,59 @@ SMALL = [  # (M, N, K, seed)
 ]
 
 
+def refusal(policy, split, M, Kd):
+    """Why the library must refuse this pinned (kernel, split factor), or None.  Pinned values are honoured or
+    refused, never silently replaced."""
+    kc = -(-Kd // 128)
+    if split > kc:
+        return "pinned split factor"
+    if policy == TC_PAIR and M <= 128:
+        return "more than 128 tokens"
+    if policy == TC_PAIR and split > 1:
+        return "pinned split factor"
+    return None
+
+
 @pytest.mark.parametrize("policy,split", [(CORE, 0), (TC_TOKEN, 1), (TC_WEIGHT, 1), (TC_TOKEN, 2), (TC_WEIGHT, 3),
-                                          (AUTO, 0)],
-                         ids=["core", "tctoken", "tcweight", "tctoken_split2", "tcweight_split3", "auto"])
+                                          (TC_PAIR, 0), (AUTO, 0)],
+                         ids=["core", "tctoken", "tcweight", "tctoken_split2", "tcweight_split3", "tcpair", "auto"])
 @pytest.mark.parametrize("M,N,Kd,seed", SMALL)
 def test_fp8_gemm_vs_oracle(K, policy, split, M, N, Kd, seed):
+    import dsv3_b200
     xq, xs, wq, ws = quantised_case(M, N, Kd, seed)
+    why = refusal(policy, split, M, Kd)
+    if why is not None:
+        with pytest.raises(dsv3_b200.Dsv3Error, match=why) as e:
+            run(K, policy, split, xq, xs, wq, ws)
+        assert e.value.status == -2      # DSV3_ERR_UNSUPPORTED
+        return
     ref = O.fp8_gemm(xq, xs, wq, ws)
     y = run(K, policy, split, xq, xs, wq, ws)
     assert y.shape == (M, N) and y.dtype == torch.bfloat16
     assert_gemm_close(y, ref)
+
+
+PAIR = [  # shapes for the CTA-pair kernel: (M, N, K, seed)
+    (129, 128, 128, 60),      # second CTA of the only pair has one valid token row; a single K chunk
+    (300, 520, 896, 61),      # odd number of token tiles (the last pair's second tile is empty), odd number of K chunks
+    (256, 1000, 1152, 62),    # N % 8 != 0 would forbid the tensor-map store: 1000 is fine, see next
+    (257, 1001, 384, 63),     # N % 8 != 0: plain stores; three token tiles
+    (640, 384, 2048, 64),
+    (1024, 576, 7168, 65),    # wkv_a: last weight tile half empty
+]
+
+
+@pytest.mark.parametrize("M,N,Kd,seed", PAIR)
+def test_fp8_gemm_cta_pair_kernel_vs_oracle_and_single_cta_kernel(K, M, N, Kd, seed):
+    xq, xs, wq, ws = quantised_case(M, N, Kd, seed)
+    ref = O.fp8_gemm(xq, xs, wq, ws)
+    y = run(K, TC_PAIR, 0, xq, xs, wq, ws)
+    assert_gemm_close(y, ref)
+    # same products, same scale factors, same order of the chunk sums: the two tcgen05 kernels agree bit for bit
+    y1 = run(K, TC_TOKEN, 1, xq, xs, wq, ws)
+    assert np.array_equal(bf16_bits(y), bf16_bits(y1))
+    # twice in a row on a warm pipeline
+    assert np.array_equal(bf16_bits(run(K, TC_PAIR, 0, xq, xs, wq, ws)), bf16_bits(y))
 
 
 def test_fp8_gemm_unaligned_k_uses_cuda_core_kernel(K):
@@ -199,6 +242,28 @@ def test_fp8_gemm_matches_gpu_reference_goldens(K, golden_gpu):
             assert_gemm_close(run(K, policy, 0, xq, xs, wq, ws), ref)
 
 
+@pytest.mark.parametrize("name,M,N,Kd,seed", [("expert_w13_m256", 256, 2048, 7168, 3), ("expert_w2_m64", 64, 7168, 2048, 4),
+                                              ("wkv_a_m1024", 1024, 576, 7168, 5), ("wq_b_tp8_m4096", 4096, 3072, 1536, 6)])
+def test_fp8_gemm_matches_gpu_reference_goldens_at_v3_shapes(K, golden_gpu, name, M, N, Kd, seed):
+    """The reference's Triton fp8_gemm on a B200 at V3 shapes (stored: digest + the first 4096 outputs).  The
+    inputs are rebuilt from their seeds; this library's act_quant must reproduce the reference's FP8 activations
+    bit for bit (digest), so the GEMM under test sees exactly what the reference's GEMM saw.  Every tcgen05
+    kernel that can take the shape is held against the reference's outputs."""
+    import hashlib
+    x, _, wq, ws = O.make_case(M, N, Kd, seed)
+    xq, xs = K.act_quant(x.cuda())
+    assert hashlib.sha256(xq.cpu().view(torch.uint8).numpy().tobytes()).hexdigest() == str(golden_gpu[f"{name}.act_quant.y.sha"])
+    assert hashlib.sha256(xs.cpu().numpy().tobytes()).hexdigest() == str(golden_gpu[f"{name}.act_quant.s.sha"])
+    head = torch.from_numpy(golden_gpu[f"{name}.fp8_gemm.c.head"].view(np.int16)).view(torch.bfloat16).float()
+    policies = [(AUTO, 0), (CORE, 0)] + ([(TC_WEIGHT, 0)] if M <= 64 else [(TC_TOKEN, 1), (TC_PAIR, 0)])
+    for policy, split in policies:
+        y = run(K, policy, split, xq, xs, wq, ws)
+        got = y.reshape(-1)[:head.numel()].float().cpu()
+        rms = y.float().pow(2).mean().sqrt().item()          # rms of the whole output (the stored slice is 2-7 rows)
+        bound = 1e-2 * (head.abs() + rms)
+        assert bool(((got - head).abs() <= bound).all()), (policy, float(((got - head).abs() / bound).max()))
+
+
 FULL = [  # V3 shapes at sizes the oracle cannot cover whole: (M, N, K, seed)
     (4096, 7168, 2048, 40),     # expert / shared w2, wo at TP=8
     (4096, 576, 7168, 41),      # wkv_a
@@ -236,3 +301,12 @@ def test_fp8_gemm_full_size_properties(K, M, N, Kd, seed):
     dsv3_b200.set_gemm_policy(AUTO, 0)
     y3 = K.fp8_gemm(xq, xs * 2, wq, ws)
     assert torch.equal(y3.float(), y.float() * 2)
+    # (4) the token-major tcgen05 kernels (one CTA per tile, CTA pairs) agree bit for bit, whichever was chosen above
+    if M > 128:
+        dsv3_b200.set_gemm_policy(TC_TOKEN, 1)
+        y4 = K.fp8_gemm(xq, xs, wq, ws)
+        dsv3_b200.set_gemm_policy(TC_PAIR, 0)
+        y5 = K.fp8_gemm(xq, xs, wq, ws)
+        assert torch.equal(y4, y5)
+        err = (y4.float() - y2.float()).abs()
+        assert bool((err <= 1e-2 * (y2.float().abs() + rms)).all())
