@@ -1,0 +1,327 @@
+"""The callers directly above the three operators, through the CUDA path, against the CPU oracle.
+
+Restated here (a few lines each, citing the reference): the FP8 branch of ``linear()`` (model.py:158-160),
+``MLP.forward`` (model.py:500-532), the projection chain of ``MLA.forward`` including the per-forward
+``weight_dequant(wkv_b)`` (model.py:461-468, 481, 496), the shard layout of ``ColumnParallelLinear`` /
+``RowParallelLinear`` (model.py:208-267), and ``MoE.forward`` with the gate of the 671B configuration
+(model.py:566-598, 669-693).  The device side calls the drop-in ``kernel`` module (and the grouped-GEMM entry
+points of the C ABI); the host side calls ``oracle.linear_fp8`` / ``oracle.fp8_gemm`` on the same seeded
+inputs.  Tolerance: the fp8_gemm bound |y - y_ref| <= 1e-2 (|y_ref| + rms(y_ref)) for a Linear whose GEMM is
+fed the device's own FP8 activations on both sides (act_quant is held bit for bit against the reference's GPU
+kernel in test_gpu_quant.py; the oracle divides exactly where a GPU uses the approximate division, which moves
+0.1-0.3 % of the FP8 codes at rounding ties).  Against a chain computed entirely on the host the element-wise
+bound cannot hold: measured on B200, the device GEMM agrees with the oracle's to a relative RMS of 1e-5 on
+identical FP8 inputs, host- and device-quantised activations give outputs 0.35 % apart (relative RMS), and after
+one more re-quantisation (a second Linear) the distance is 1.4-1.8 %, because an input that differs by half a
+percent lands on a different 3-bit-mantissa FP8 code in about one element in twenty and a code step is 6-12 % of
+the value.  That amplification is a property of 1x128 FP8 quantisation, not of either implementation.  Chains
+are therefore held to a relative RMS error of 3e-2 plus a loose element-wise guard, single Linears to 5e-3.
+"""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+from oracle import oracle as O
+from gpu_util import assert_gemm_close, bf16_bits
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True)
+def _bf16_default():
+    import dsv3_b200
+    torch.set_default_dtype(torch.bfloat16)
+    yield
+    torch.set_default_dtype(torch.float32)
+    dsv3_b200.set_gemm_policy(0, 0)
+    dsv3_b200.check_device_status()
+
+
+def gpu_weight(N, K, seed):
+    """N(0, 0.02) weight generated and block-quantised on the device (the device quantiser equals the oracle's bit
+    for bit: test_gpu_quant.py); returns device and host copies."""
+    import dsv3_b200
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    w = (torch.randn(N, K, generator=g, device="cuda", dtype=torch.float32) * 0.02).to(torch.bfloat16)
+    wq, ws = dsv3_b200.weight_quant(w)
+    return wq, ws, wq.cpu(), ws.cpu()
+
+
+def linear_gpu(x, wq, ws):
+    """model.py:158-160 on the drop-in module."""
+    import kernel
+    xq, xs = kernel.act_quant(x)
+    return kernel.fp8_gemm(xq, xs, wq, ws)
+
+
+def linear_ref(x, wq_h, ws_h):
+    """The oracle's GEMM on the FP8 activations the device produces for x."""
+    import kernel
+    xq, xs = kernel.act_quant(x if x.is_cuda else x.cuda())
+    return O.fp8_gemm(xq.cpu(), xs.cpu(), wq_h, ws_h)
+
+
+def close(y, ref, rel):
+    ok, ratio = O.gemm_tolerance_ok(y, ref, rel)
+    assert ok, f"worst |err| / bound = {ratio:.3f} (rel {rel})"
+
+
+def chain_close(y, ref, rel_rms=3e-2, guard=2e-1):
+    """Relative RMS error of a chain of Linears against the all-host chain, plus a loose element-wise guard."""
+    yr = ref.float()
+    err = y.float().cpu() - yr
+    rr = (err.pow(2).mean().sqrt() / yr.pow(2).mean().sqrt()).item()
+    assert rr <= rel_rms, f"relative RMS error {rr:.4f} > {rel_rms}"
+    close(y, ref, guard)
+
+
+# ---------------------------------------------------------------------------------------------------------
+# MLP.forward (model.py:500-532): w2(silu(w1 x) * w3 x)
+# ---------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("T,dim,inter", [(5, 7168, 2304), (200, 2048, 1408), (64, 7168, 2048)],
+                         ids=["dense_tp8_decode", "16B_expert_prefill", "expert_m64"])
+def test_mlp_forward_chain(T, dim, inter):
+    x = O.randn_bf16((T, dim), 900 + T, 1.0)
+    w1 = gpu_weight(inter, dim, 1)
+    w3 = gpu_weight(inter, dim, 2)
+    w2 = gpu_weight(dim, inter, 3)
+    xd = x.cuda()
+    h1, h3 = linear_gpu(xd, w1[0], w1[1]), linear_gpu(xd, w3[0], w3[1])
+    close(h1, linear_ref(x, w1[2], w1[3]), 1e-2)
+    close(h3, linear_ref(x, w3[2], w3[3]), 1e-2)
+    chain_close(h1, O.linear_fp8(x, w1[2], w1[3]), 5e-3)
+    h = F.silu(h1) * h3
+    # the second Linear on the device's own hidden state: isolates w2 from upstream rounding
+    y = linear_gpu(h, w2[0], w2[1])
+    close(y, linear_ref(h, w2[2], w2[3]), 1e-2)
+    # the whole chain on the host
+    href = F.silu(O.linear_fp8(x, w1[2], w1[3])) * O.linear_fp8(x, w3[2], w3[3])
+    chain_close(y, O.linear_fp8(href, w2[2], w2[3]))
+
+
+# ---------------------------------------------------------------------------------------------------------
+# MLA.forward's projections (model.py:461-468, 481, 496) at the 671B dims of one TP=8 rank
+# ---------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("T", [3, 160], ids=["decode", "prefill"])
+def test_mla_projection_chain(T):
+    import kernel
+    dim, q_lora, kv_lora, rope, heads, nope, vdim = 7168, 1536, 512, 64, 16, 128, 128     # 128 heads / 8 ranks
+    x = O.randn_bf16((T, dim), 950 + T, 1.0)
+    wq_a = gpu_weight(q_lora, dim, 11)
+    wq_b = gpu_weight(heads * (nope + rope), q_lora, 12)
+    wkv_a = gpu_weight(kv_lora + rope, dim, 13)                   # N = 576: the last weight tile is half empty
+    wkv_b = gpu_weight(heads * (nope + vdim), kv_lora, 14)
+    wo = gpu_weight(dim, heads * vdim, 15)
+    qn = torch.ones(q_lora, dtype=torch.bfloat16)
+    xd = x.cuda()
+    # q = wq_b(q_norm(wq_a(x)))                                    model.py:464
+    qa = linear_gpu(xd, wq_a[0], wq_a[1])
+    qa_ref = O.linear_fp8(x, wq_a[2], wq_a[3])
+    close(qa, linear_ref(x, wq_a[2], wq_a[3]), 1e-2)
+    chain_close(qa, qa_ref, 5e-3)
+    qa_n = F.rms_norm(qa, (q_lora,), qn.cuda(), 1e-6)
+    q = linear_gpu(qa_n, wq_b[0], wq_b[1])
+    close(q, linear_ref(qa_n, wq_b[2], wq_b[3]), 1e-2)
+    chain_close(q, O.linear_fp8(F.rms_norm(qa_ref, (q_lora,), qn, 1e-6), wq_b[2], wq_b[3]))
+    # kv = wkv_a(x)                                                model.py:468
+    kv = linear_gpu(xd, wkv_a[0], wkv_a[1])
+    close(kv, linear_ref(x, wkv_a[2], wkv_a[3]), 1e-2)
+    chain_close(kv, O.linear_fp8(x, wkv_a[2], wkv_a[3]), 5e-3)
+    # wkv_b = weight_dequant(self.wkv_b.weight, self.wkv_b.scale)  model.py:481 -- bit exact
+    wd = kernel.weight_dequant(wkv_b[0], wkv_b[1])
+    assert np.array_equal(bf16_bits(wd), bf16_bits(O.weight_dequant(wkv_b[2], wkv_b[3])))
+    # x = wo(x.flatten(2))                                         model.py:496 (this rank's partial sum)
+    a = O.randn_bf16((T, heads * vdim), 960 + T, 1.0)
+    close(linear_gpu(a.cuda(), wo[0], wo[1]), linear_ref(a, wo[2], wo[3]), 1e-2)
+
+
+# ---------------------------------------------------------------------------------------------------------
+# ColumnParallelLinear / RowParallelLinear shards (model.py:208-267) on one GPU against the unsharded oracle
+# ---------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("ws", [2, 8])
+def test_column_and_row_parallel_shards_against_unsharded_oracle(ws):
+    T, K, N = 48, 2048, 1024
+    x = O.randn_bf16((T, K), 970, 1.0)
+    w = O.randn_bf16((N, K), 971, 0.02)
+    wq, wsc = O.weight_quant(w)
+    full = O.linear_fp8(x, wq, wsc)
+    # column parallel: rank r owns rows [r N/ws, (r+1) N/ws) of W and of the scale rows; outputs concatenate
+    part = N // ws
+    cols = []
+    for r in range(ws):
+        wq_r = wq[r * part:(r + 1) * part].contiguous()
+        ws_r = wsc[r * part // 128:(r + 1) * part // 128].contiguous()
+        cols.append(linear_gpu(x.cuda(), wq_r.cuda(), ws_r.cuda()))
+    close(torch.cat(cols, dim=1), linear_ref(x, wq, wsc), 1e-2)
+    chain_close(torch.cat(cols, dim=1), full, 5e-3)
+    # row parallel: rank r owns columns [r K/ws, (r+1) K/ws) of W (and of the scale columns) and the matching slice
+    # of the activation; the bf16 partial outputs are summed (all_reduce, model.py:263-264)
+    kpart = K // ws
+    partial_gpu, partial_ref = [], []
+    for r in range(ws):
+        wq_r = wq[:, r * kpart:(r + 1) * kpart].contiguous()
+        ws_r = wsc[:, r * kpart // 128:(r + 1) * kpart // 128].contiguous()
+        x_r = x[:, r * kpart:(r + 1) * kpart].contiguous()
+        y_r = linear_gpu(x_r.cuda(), wq_r.cuda(), ws_r.cuda())
+        ref_r = linear_ref(x_r, wq_r, ws_r)
+        close(y_r, ref_r, 1e-2)
+        partial_gpu.append(y_r.float().cpu())
+        partial_ref.append(ref_r.float())
+    total = torch.stack(partial_gpu).sum(0).to(torch.bfloat16)
+    total_ref = torch.stack(partial_ref).sum(0).to(torch.bfloat16)
+    close(total, total_ref, 1e-2)
+    # quantising K/ws-wide slices is the same arithmetic as quantising the whole row (1 x 128 blocks), so the sum of
+    # the partials equals the unsharded result up to the bf16 rounding of each partial
+    chain_close(total, full, 1e-2)
+
+
+# ---------------------------------------------------------------------------------------------------------
+# Grouped GEMM over per-expert weights at V3 dims, per segment against the oracle
+# ---------------------------------------------------------------------------------------------------------
+def _grouped(lib, _lib, weights, a_q, a_s, seg, N, K):
+    n = len(weights)
+    table = torch.empty(lib.dsv3_group_table_bytes(n), dtype=torch.uint8, device="cuda")
+    wp = (ctypes.c_void_p * n)(*[w[0].data_ptr() for w in weights])
+    sp = (ctypes.c_void_p * n)(*[w[1].data_ptr() for w in weights])
+    st = torch.cuda.current_stream().cuda_stream
+    _lib.check(lib.dsv3_group_table_build(table.data_ptr(), wp, sp, n, N, K, st))
+    rows = a_q.size(0)
+    c = torch.full((rows, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    _lib.check(lib.dsv3_fp8_gemm_grouped(table.data_ptr(), n, a_q.data_ptr(), a_s.data_ptr(), seg.data_ptr(), rows, N, K,
+                                         c.data_ptr(), st))
+    torch.cuda.synchronize()
+    return c
+
+
+@pytest.mark.parametrize("N,K", [(2048, 7168), (7168, 2048)], ids=["w13", "w2"])
+def test_grouped_gemm_per_segment_vs_oracle_at_v3_dims(N, K):
+    """32 local experts (the TP=8 share of 256) with empty, one-row, one-tile and several-tile segments."""
+    from dsv3_b200 import _lib
+    import kernel
+    lib = _lib.lib
+    n = 32
+    counts = [0, 1, 64, 65, 0, 130, 3, 17] + [0] * 8 + [2, 0, 31, 1] + [0] * 11 + [200]
+    assert len(counts) == n
+    seg_h = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+    rows = int(seg_h[-1]) + 40                                     # rows beyond seg[n] belong to other ranks' experts
+    weights = [gpu_weight(N, K, 2000 + e) for e in range(n)]
+    x = O.randn_bf16((rows, K), 990 + N, 1.0)
+    a_q, a_s = kernel.act_quant(x.cuda())
+    seg = torch.from_numpy(seg_h).cuda()
+    c = _grouped(lib, _lib, weights, a_q, a_s, seg, N, K)
+    a_qh, a_sh = a_q.cpu(), a_s.cpu()
+    for e in range(n):
+        lo, hi = int(seg_h[e]), int(seg_h[e + 1])
+        if hi == lo:
+            continue
+        ref = O.fp8_gemm(a_qh[lo:hi].contiguous(), a_sh[lo:hi].contiguous(), weights[e][2], weights[e][3])
+        assert_gemm_close(c[lo:hi], ref)
+    assert bool(torch.isnan(c[int(seg_h[-1]):].float()).all()), "rows beyond seg[n] must not be written"
+
+
+# ---------------------------------------------------------------------------------------------------------
+# MoE.forward with the 671B gate (model.py:566-598, 669-693), one TP=8 rank's 32 experts
+# ---------------------------------------------------------------------------------------------------------
+class _Lin:
+    scale_fmt = None
+
+    def __init__(self, N, K, seed):
+        self.weight, sc, self.wq_h, self.ws_h = gpu_weight(N, K, seed)
+        self.weight.scale = sc
+
+    def __call__(self, x):
+        return linear_gpu(x, self.weight, self.weight.scale)
+
+    def host(self, x):
+        return O.linear_fp8(x, self.wq_h, self.ws_h)
+
+
+class _Expert:
+    def __init__(self, dim, inter, seed):
+        self.w1, self.w2, self.w3 = _Lin(inter, dim, seed), _Lin(dim, inter, seed + 1), _Lin(inter, dim, seed + 2)
+
+    def __call__(self, x):
+        return self.w2(F.silu(self.w1(x)) * self.w3(x))
+
+    def host(self, x):                                             # Expert.forward, model.py:633
+        return self.w2.host(F.silu(self.w1.host(x)) * self.w3.host(x))
+
+
+class _MoE:
+    """Attribute names of model.py's MoE (model.py:636-666); gate = Gate.forward of the 671B config (model.py:576-598):
+    sigmoid scores, per-expert bias, 8 groups of which the 4 best (by the sum of their two best scores) stay,
+    top-8, weights renormalised and scaled by 2.5."""
+
+    def __init__(self, dim, inter, n_routed, start, end, seed):
+        self.dim, self.n_routed_experts, self.n_activated_experts = dim, n_routed, 8
+        self.n_groups, self.topk_groups, self.route_scale = 8, 4, 2.5
+        self.n_local_experts = end - start
+        self.experts_start_idx, self.experts_end_idx = start, end
+        self.experts = [_Expert(dim, inter, seed + 10 * i) if start <= i < end else None for i in range(n_routed)]
+        g = torch.Generator(device="cuda").manual_seed(seed)
+        self.gate_w = (torch.randn(n_routed, dim, generator=g, device="cuda", dtype=torch.float32) * 0.02).bfloat16()
+        self.gate_b = torch.randn(n_routed, generator=g, device="cuda", dtype=torch.float32) * 0.01
+        self.shared = _Expert(dim, inter // 8, seed + 5000)        # the TP=8 slice of the shared expert
+        self._routing = None
+
+    def gate(self, x):
+        if self._routing is None:
+            scores = F.linear(x, self.gate_w).sigmoid()
+            original = scores
+            sc = (scores + self.gate_b).view(x.size(0), self.n_groups, -1)
+            group_scores = sc.topk(2, dim=-1)[0].sum(dim=-1)
+            idx = group_scores.topk(self.topk_groups, dim=-1)[1]
+            mask = sc.new_ones(x.size(0), self.n_groups, dtype=torch.bool).scatter_(1, idx, False)
+            sc = sc.masked_fill(mask.unsqueeze(-1), float("-inf")).flatten(1)
+            indices = torch.topk(sc, self.n_activated_experts, dim=-1)[1]
+            weights = original.gather(1, indices)
+            weights = weights / weights.sum(dim=-1, keepdim=True) * self.route_scale
+            self._routing = (weights.type_as(x), indices)
+        return self._routing
+
+    def shared_experts(self, x):
+        return self.shared(x)
+
+    def host_forward(self, x, weights, indices):
+        """MoE.forward (model.py:669-693) on the host with the routing the device computed (a CPU bf16 gate GEMM
+        could break near-ties the other way; the routing itself is checked in test_gpu_moe.py)."""
+        y = torch.zeros_like(x)
+        counts = torch.bincount(indices.flatten(), minlength=self.n_routed_experts).tolist()
+        for i in range(self.experts_start_idx, self.experts_end_idx):
+            if counts[i] == 0:
+                continue
+            idx, top = torch.where(indices == i)
+            y[idx] += self.experts[i].host(x[idx]) * weights[idx, top, None]
+        return y, y + self.shared.host(x)
+
+
+def test_grouped_moe_forward_v3_dims_vs_host_restatement():
+    import dsv3_b200
+    from dsv3_b200 import linear_seam as L
+    T, dim, inter, E = 96, 7168, 2048, 256
+    moe = _MoE(dim, inter, E, 64, 96, seed=300)                    # rank 2 of 8: experts 64..95
+    x = O.randn_bf16((T, dim), 301, 1.0)
+    L.reset_memo()
+    out = dsv3_b200.grouped_moe_forward(moe, x.cuda())
+    dsv3_b200.check_device_status()
+    weights, indices = moe.gate(None)
+    n_local_pairs = int(((indices >= 64) & (indices < 96)).sum())
+    assert n_local_pairs > 0
+    y_ref, out_ref = moe.host_forward(x, weights.cpu(), indices.cpu())
+    # three chained Linears per expert and up to eight bf16 accumulation steps per token
+    chain_close(out, out_ref)
+    # the reference's own loop on the drop-in operators gives the same rounding points as the grouped path
+    yd = torch.zeros(T, dim, dtype=torch.bfloat16, device="cuda")
+    xd = x.cuda()
+    counts = torch.bincount(indices.flatten(), minlength=E).tolist()
+    for i in range(64, 96):
+        if counts[i] == 0:
+            continue
+        idx, top = torch.where(indices == i)
+        yd[idx] += moe.experts[i](xd[idx]) * weights[idx, top, None]
+    chain_close(yd, y_ref)
+    # grouped path against the reference's loop on the same device operators: same FP8 codes, same rounding points
+    close(out, (yd + moe.shared_experts(xd)).cpu(), 1e-2)
