@@ -159,8 +159,8 @@ int dsv3_weight_quant(const void* w, int64_t N, int64_t K, void* q, float* s, ds
 }
 
 int dsv3_set_gemm_policy(int kernel, int split_k) {
-    if (kernel < 0 || kernel > 4 || split_k < 0 || split_k > 64) {
-        set_last_error("set_gemm_policy: kernel must be 0..4 and split_k 0..64");
+    if (kernel < 0 || kernel > 5 || split_k < 0 || split_k > 64) {
+        set_last_error("set_gemm_policy: kernel must be 0..5 and split_k 0..64");
         return DSV3_ERR_INVALID_ARGUMENT;
     }
     g_force_kernel = kernel;
@@ -169,7 +169,8 @@ int dsv3_set_gemm_policy(int kernel, int split_k) {
 }
 
 size_t dsv3_fp8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K) {
-    if (M <= 0 || N <= 0 || K <= 0 || g_force_kernel == 1 || (K % 16) != 0) return 0;
+    if (M <= 0 || N <= 0 || K <= 0 || g_force_kernel == 1 || g_force_kernel == 5 || (K % 16) != 0) return 0;
+    if (g_force_kernel == 0 && g_force_split == 0 && M <= 8 && N >= 2048 && N * K <= (6ll << 20)) return 0;   // decode kernel
     const TcPlan pl = tc_plan(M, N, K, g_force_kernel, g_force_split);
     if (pl.error != DSV3_OK) return 0;     // dsv3_fp8_gemm reports the reason
     return tc_workspace_bytes(pl, M, N);
@@ -191,6 +192,19 @@ int dsv3_fp8_gemm(const void* a, const float* a_s, const void* b, const float* b
         DSV3_CUDA_TRY(cudaMemsetAsync(c, 0, static_cast<size_t>(M) * N * 2, st));
         return DSV3_OK;
     }
+    if (g_force_kernel == 5) {
+        if (!small_linear_supported(a, b, c, M, N, K, false)) {
+            set_last_error("fp8_gemm: the decode kernel needs M <= 16, K %% 16 == 0 and 16-byte aligned a and b");
+            return DSV3_ERR_UNSUPPORTED;
+        }
+        return launch_fp8_linear_small(nullptr, a, a_s, b, b_s, M, N, K, DSV3_SCALE_FMT_FP32, c, st);
+    }
+    // Automatic choice, decode-sized problems with a few megabytes of weights in many rows: the register-streaming
+    // kernel has less to set up than the tcgen05 pipeline (measured on B200 at M = 1..8: N 3072 x K 1536: 4.5-4.8 vs
+    // 5.9-6.0 us; N 4096 x K 512: 3.4 vs 3.8 us; at 11 MB and more the two are level or the tcgen05 kernel is ahead).
+    if (g_force_kernel == 0 && g_force_split == 0 && M <= 8 && N >= 2048 && N * K <= (6ll << 20) &&
+        small_linear_supported(a, b, c, M, N, K, false))
+        return launch_fp8_linear_small(nullptr, a, a_s, b, b_s, M, N, K, DSV3_SCALE_FMT_FP32, c, st);
     const bool tc_ok = tc_supported(a, b, c, M, N, K);
     if (g_force_kernel == 1 || (!tc_ok && g_force_kernel == 0))
         return launch_fp8_gemm_simple(a, a_s, b, b_s, M, N, K, c, st);
@@ -201,6 +215,29 @@ int dsv3_fp8_gemm(const void* a, const float* a_s, const void* b, const float* b
     const TcPlan pl = tc_plan(M, N, K, g_force_kernel, g_force_split);
     if (pl.error != DSV3_OK) return pl.error;
     return launch_fp8_gemm_tc(a, a_s, b, b_s, M, N, K, c, workspace, workspace_bytes, pl, st);
+}
+
+int dsv3_fp8_linear(const void* x, int64_t M, int64_t K, const void* w, const float* w_s, int64_t N, int scale_fmt, void* c,
+                    dsv3_stream_t stream) {
+    if (M < 0 || N < 0 || K < 0) {
+        set_last_error("fp8_linear: negative size");
+        return DSV3_ERR_INVALID_ARGUMENT;
+    }
+    if (scale_fmt != DSV3_SCALE_FMT_FP32 && scale_fmt != DSV3_SCALE_FMT_UE8M0) {
+        set_last_error("fp8_linear: unknown scale_fmt %d", scale_fmt);
+        return DSV3_ERR_INVALID_ARGUMENT;
+    }
+    if (M == 0 || N == 0) return DSV3_OK;
+    if (is_null(x) || is_null(w) || is_null(w_s) || is_null(c)) {
+        set_last_error("fp8_linear: null pointer");
+        return DSV3_ERR_INVALID_ARGUMENT;
+    }
+    if (!small_linear_supported(x, w, c, M, N, K, true)) {
+        set_last_error("fp8_linear: takes 1..16 rows, K %% 128 == 0 and 16-byte aligned x and w (M=%lld K=%lld); use "
+                       "dsv3_act_quant + dsv3_fp8_gemm otherwise", (long long)M, (long long)K);
+        return DSV3_ERR_UNSUPPORTED;
+    }
+    return launch_fp8_linear_small(x, nullptr, nullptr, w, w_s, M, N, K, scale_fmt, c, static_cast<cudaStream_t>(stream));
 }
 
 int dsv3_check_device_status(dsv3_stream_t stream, uint32_t detail[4]) {

@@ -36,6 +36,12 @@ bool tm_pair_supported(int64_t M, int64_t N, int64_t K, bool forced);
 int launch_fp8_gemm_tm(const void* a, const float* a_s, const void* b, const float* b_s, int64_t M, int64_t N,
                        int64_t K, void* c, cudaStream_t stream);
 
+// Decode-sized Linear without tcgen05 set-up (fp8_linear_small.cu): M <= 16; x != nullptr quantises bf16 activations
+// in the kernel's prologue (K % 128 == 0), otherwise (a, a_s) are the quantised activations (K % 16 == 0).
+bool small_linear_supported(const void* act, const void* w, const void* c, int64_t M, int64_t N, int64_t K, bool fused);
+int launch_fp8_linear_small(const void* x, const void* a, const float* a_s, const void* w, const float* w_s, int64_t M,
+                            int64_t N, int64_t K, int scale_fmt, void* c, cudaStream_t stream);
+
 // Grouped GEMM over per-group weights (MoE experts).
 size_t group_table_bytes(int n);
 int build_group_table(void* table_dev, const void* const* weights, const float* const* scales, int n, int64_t N,

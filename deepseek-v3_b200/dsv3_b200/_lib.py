@@ -25,6 +25,7 @@ EXPORTS = (
     "dsv3_fp8_gemm_workspace_bytes", "dsv3_fp8_gemm", "dsv3_set_gemm_policy", "dsv3_weight_quant",
     "dsv3_check_device_status", "dsv3_fp8_gemm_static", "dsv3_fp8_gemm_static_scratch_bytes",
     "dsv3_group_table_bytes", "dsv3_group_table_build", "dsv3_fp8_gemm_grouped", "dsv3_moe_combine", "dsv3_moe_route",
+    "dsv3_fp8_linear",
 )
 
 
@@ -50,6 +51,8 @@ def _load() -> ctypes.CDLL:
     lib.dsv3_fp8_gemm_workspace_bytes.argtypes = [i64, i64, i64]
     lib.dsv3_fp8_gemm_workspace_bytes.restype = sz
     lib.dsv3_fp8_gemm.argtypes = [vp, vp, vp, vp, i64, i64, i64, vp, vp, sz, vp]
+    lib.dsv3_fp8_linear.argtypes = [vp, i64, i64, vp, vp, i64, ci, vp, vp]
+    lib.dsv3_fp8_linear.restype = ci
     lib.dsv3_fp8_gemm_static.argtypes = [vp, vp, vp, vp, i64, i64, i64, vp, vp]
     lib.dsv3_fp8_gemm_static.restype = ci
     lib.dsv3_fp8_gemm_static_scratch_bytes.restype = sz

@@ -8,10 +8,21 @@
     dsv3_b200.install_linear(model)
 
 redirects all of them without touching the file.  The replacement keeps the reference's three
-branches and adds one thing: the FP8 quantisation of an activation tensor is remembered while that
-tensor is alive and unmodified, so that Linears fed the same input (``wq_a``/``wkv_a`` in MLA,
-``w1``/``w3`` in MLP and Expert) quantise it once instead of twice.  Results are bit-identical to
-the unfused path because the very same ``act_quant`` output is reused.
+branches and changes how the FP8 branch is launched:
+
+* at most 4 rows (a decode step at small batch) and at most 16 MB of weights: one launch, the activations are
+  quantised in the GEMM's prologue (``fp8_linear``) instead of ``act_quant`` followed by ``fp8_gemm`` and an FP8
+  round trip through HBM;
+* more rows: the quantisation of an activation tensor is remembered while that tensor is alive and unmodified,
+  so that Linears fed the same input (``wq_a``/``wkv_a`` in MLA, ``w1``/``w3`` in MLP and Expert) quantise it
+  once.  Results are bit-identical to the unfused path because the very same ``act_quant`` output is reused.
+
+The memo holds the two most recent inputs (``wq_a(x)``, ``wq_b(q_norm(..))``, ``wkv_a(x)`` of model.py:464-468
+touch two tensors alternately).  An entry is reused only for the same tensor object, on the same CUDA stream,
+with an unchanged in-place modification counter.  Tensors created under ``torch.inference_mode()`` have no such
+counter: for them the memo is off unless ``assume_no_inplace=True`` is passed to ``install_linear`` -- the host
+then promises not to modify a projection's input in place between two Linears (the reference's model.py never
+does).
 """
 from __future__ import annotations
 
@@ -21,33 +32,41 @@ from typing import Optional
 import torch
 import torch.nn.functional as F
 
-from .ops import act_quant, fp8_gemm, weight_dequant
+from .ops import (act_quant, fp8_gemm, fp8_linear, weight_dequant, FUSED_LINEAR_MAX_ROWS, FUSED_LINEAR_MAX_WEIGHT_BYTES,
+                  _stream)
 
-_memo = {"ref": None, "version": -1, "key": None, "value": None}
-stats = {"act_quant_calls": 0, "act_quant_reused": 0}
+_memo = []          # at most two entries, most recent first: dicts with ref / version / key / value
+stats = {"act_quant_calls": 0, "act_quant_reused": 0, "fused_linear_calls": 0}
+_assume_no_inplace = False
 
 
-def _version(x: torch.Tensor) -> int:
-    """In-place modification counter; tensors created under torch.inference_mode() have none, and there
-    the memo relies on object identity alone (model.py does not modify a projection's input in place)."""
+def _version(x: torch.Tensor) -> Optional[int]:
+    """In-place modification counter, or None for tensors that have none (inference mode)."""
     try:
         return x._version
     except RuntimeError:
-        return -2
+        return None
 
 
 def _quantised(x: torch.Tensor, block_size: int, scale_fmt: Optional[str]):
-    ref = _memo["ref"]
-    key = (x.data_ptr(), tuple(x.shape), block_size, scale_fmt)
-    if ref is not None and ref() is x and _memo["version"] == _version(x) and _memo["key"] == key:
-        stats["act_quant_reused"] += 1
-        return _memo["value"]
+    ver = _version(x)
+    if ver is None and not _assume_no_inplace:
+        stats["act_quant_calls"] += 1
+        return act_quant(x, block_size, scale_fmt)
+    key = (x.data_ptr(), tuple(x.shape), block_size, scale_fmt, _stream())
+    for i, e in enumerate(_memo):
+        if e["ref"]() is x and e["version"] == ver and e["key"] == key:
+            stats["act_quant_reused"] += 1
+            if i:
+                _memo.insert(0, _memo.pop(i))
+            return e["value"]
     value = act_quant(x, block_size, scale_fmt)
     stats["act_quant_calls"] += 1
     try:
-        _memo.update(ref=weakref.ref(x), version=_version(x), key=key, value=value)
+        _memo.insert(0, dict(ref=weakref.ref(x), version=ver, key=key, value=value))
+        del _memo[2:]
     except TypeError:           # tensor subclasses that cannot be weakly referenced: no memo
-        _memo.update(ref=None, value=None)
+        pass
     return value
 
 
@@ -58,16 +77,26 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
         return F.linear(x, weight, bias)
     if gemm_impl == "bf16":
         return F.linear(x, weight_dequant(weight, weight.scale), bias)
-    xq, xs = _quantised(x, block_size, scale_fmt)
-    y = fp8_gemm(xq, xs, weight, weight.scale)
+    K = x.size(-1)
+    rows = x.numel() // K if K else 0
+    if (0 < rows <= FUSED_LINEAR_MAX_ROWS and weight.numel() <= FUSED_LINEAR_MAX_WEIGHT_BYTES and block_size == 128
+            and K % 128 == 0 and x.dtype == torch.bfloat16 and x.is_contiguous()):
+        stats["fused_linear_calls"] += 1
+        y = fp8_linear(x, weight, weight.scale, scale_fmt)
+    else:
+        xq, xs = _quantised(x, block_size, scale_fmt)
+        y = fp8_gemm(xq, xs, weight, weight.scale)
     if bias is not None:
         y += bias
     return y
 
 
-def install_linear(model_module) -> None:
+def install_linear(model_module, assume_no_inplace: bool = False) -> None:
     """Point ``model_module.linear`` at this implementation; ``model_module.gemm_impl`` and
     ``model_module.block_size`` keep their meaning and are read at call time, as in the reference."""
+    global _assume_no_inplace
+    _assume_no_inplace = bool(assume_no_inplace)
+
     def _linear(x, weight, bias=None, scale_fmt=None):
         return linear(x, weight, bias, scale_fmt, gemm_impl=model_module.gemm_impl,
                       block_size=model_module.block_size)
@@ -76,5 +105,5 @@ def install_linear(model_module) -> None:
 
 
 def reset_memo() -> None:
-    _memo.update(ref=None, version=-1, key=None, value=None)
-    stats.update(act_quant_calls=0, act_quant_reused=0)
+    del _memo[:]
+    stats.update(act_quant_calls=0, act_quant_reused=0, fused_linear_calls=0)

@@ -83,6 +83,21 @@ int dsv3_fp8_gemm(const void* a, const float* a_s, const void* b, const float* b
                   void* workspace, size_t workspace_bytes, dsv3_stream_t stream);
 
 /*
+ * Decode-sized Linear in one launch -- replaces the FP8 branch of linear(), model.py:158-160
+ * (`y = fp8_gemm(*act_quant(x, block_size, scale_fmt), weight, weight.scale)`), for at most 16 rows.
+ *   x : bf16 [M, K], 1 <= M <= 16, K % 128 == 0      w : e4m3 [N, K]      w_s : fp32 [ceil(N/128), K/128]
+ *   c : bf16 [M, N]
+ * The activations are quantised in the kernel's prologue with the arithmetic of dsv3_act_quant (the FP8 codes
+ * and scales the GEMM consumes are bit-identical to what dsv3_act_quant would have written), each 128-wide chunk
+ * product is scaled as the reference does (acc += (dot * a_s) * b_s, kernel.py:162), K is split across warps and
+ * CTA clusters and summed in a fixed order: the result is deterministic and lies within the fp8_gemm tolerance
+ * of dsv3_act_quant followed by dsv3_fp8_gemm (the order of the fp32 partial sums differs).  No workspace.
+ * Other shapes return DSV3_ERR_UNSUPPORTED: call the two operators instead.
+ */
+int dsv3_fp8_linear(const void* x, int64_t M, int64_t K, const void* w, const float* w_s, int64_t N,
+                    int scale_fmt, void* c, dsv3_stream_t stream);
+
+/*
  * fp8_gemm for hosts that have no device memory to lend -- no counterpart in the reference, whose
  * Python wrapper simply lets torch allocate.  Same arithmetic and the same kernels as dsv3_fp8_gemm,
  * but the split-K scratch is a fixed array of DSV3_STATIC_SCRATCH_BYTES inside the library image, so the
@@ -110,7 +125,8 @@ int dsv3_fp8_gemm_static(const void* a, const float* a_s, const void* b, const f
  *   0 = automatic (default), 1 = CUDA-core tiled kernel (any shape),
  *   2 = tcgen05 kernel, tokens on the MMA M axis, one CTA per 128 x 128 tile,
  *   3 = tcgen05 kernel, weights on the MMA M axis (small M),
- *   4 = tcgen05 kernel, tokens on the MMA M axis, CTA pairs on 256 x 128 tiles (needs M > 128, no split-K).
+ *   4 = tcgen05 kernel, tokens on the MMA M axis, CTA pairs on 256 x 128 tiles (needs M > 128, no split-K),
+ *   5 = decode kernel (warp-level FP8 MMA on weights streamed through registers; needs M <= 16).
  * split_k = 0 lets the library choose.  A pinned kernel or split factor is honoured or the GEMM call fails
  * with DSV3_ERR_UNSUPPORTED (shape the kernel cannot take, split factor that does not fit); it is never
  * silently replaced.  The setting is one process-wide pair of integers read by every later dsv3_fp8_gemm /

@@ -32,7 +32,7 @@ def test_linear_seam_matches_unfused_path_and_reuses_quantisation():
         L.reset_memo()
         y1 = L.linear(x, q1)
         y3 = L.linear(x, q3)                       # same input object: quantised once
-        assert L.stats == {"act_quant_calls": 1, "act_quant_reused": 1}
+        assert L.stats == {"act_quant_calls": 1, "act_quant_reused": 1, "fused_linear_calls": 0}
         xq, xs = kernel.act_quant(x)
         assert np.array_equal(bf16_bits(y1), bf16_bits(kernel.fp8_gemm(xq, xs, q1, q1.scale)))
         assert np.array_equal(bf16_bits(y3), bf16_bits(kernel.fp8_gemm(xq, xs, q3, q3.scale)))
@@ -45,6 +45,30 @@ def test_linear_seam_matches_unfused_path_and_reuses_quantisation():
         # a different tensor does too, even with equal contents
         L.linear(x.clone(), q1)
         assert L.stats["act_quant_calls"] == 3
+        # two inputs used alternately, as wq_a(x), wq_b(q), wkv_a(x) of model.py:464-468: both stay remembered
+        L.reset_memo()
+        x2 = O.randn_bf16((35, 512), 74, 1.0).cuda()
+        L.linear(x, q1); L.linear(x2, q3); L.linear(x, q3); L.linear(x2, q1)
+        assert (L.stats["act_quant_calls"], L.stats["act_quant_reused"]) == (2, 2)
+        # tensors made under inference_mode carry no modification counter: no memo unless the host vouches for them
+        L.reset_memo()
+        with torch.inference_mode():
+            xi = O.randn_bf16((40, 512), 75, 1.0).cuda()
+            a1 = L.linear(xi, q1); L.linear(xi, q3)
+            assert (L.stats["act_quant_calls"], L.stats["act_quant_reused"]) == (2, 0)
+            fake_i = types.SimpleNamespace(gemm_impl="fp8", block_size=128, linear=None)
+            dsv3_b200.install_linear(fake_i, assume_no_inplace=True)
+            a2 = fake_i.linear(xi, q1); fake_i.linear(xi, q3)
+            assert (L.stats["act_quant_calls"], L.stats["act_quant_reused"]) == (3, 1)
+            assert torch.equal(a1, a2)
+            dsv3_b200.install_linear(fake_i)
+        # a few rows: one fused launch, no separate act_quant; within the GEMM tolerance of the two-operator path
+        L.reset_memo()
+        xs4 = O.randn_bf16((2, 2, 512), 76, 1.0).cuda()
+        yf = L.linear(xs4, q1)
+        assert L.stats == {"act_quant_calls": 0, "act_quant_reused": 0, "fused_linear_calls": 1}
+        xq4, xs4s = kernel.act_quant(xs4)
+        assert_gemm_close(yf.reshape(4, 384), kernel.fp8_gemm(xq4, xs4s, q1, q1.scale).reshape(4, 384).cpu())
         # bias, bf16 weights and the bf16 GEMM mode follow model.py:153-157
         b = torch.randn(384, device="cuda")
         assert torch.equal(L.linear(x, q1, b), L.linear(x, q1) + b)
