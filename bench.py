@@ -33,7 +33,7 @@ for _p in (ROOT, os.path.join(ROOT, "deepseek-v3_b200")):
         sys.path.insert(0, _p)
 
 MS = [1, 8, 32, 64, 256, 1024, 4096, 16384]
-# name, K (in), N (out), parallel kind under tensor parallelism (model.py:208-267, SURVEY appendix B)
+# name, K (in), N (out), parallel kind under tensor parallelism (model.py:208-267)
 BASE_SHAPES = [
     ("wq_a", 7168, 1536, "replicated"),
     ("wq_b", 1536, 24576, "column"),
@@ -78,7 +78,8 @@ def sweep_rows(world: int, rank: int = 0):
         return rows
     rows = []
     owner = 0
-    for s in BASE_SHAPES:
+    # row-parallel Linears first: their all_reduce is issued on a communication stream and overlaps the GEMMs after them
+    for s in sorted(BASE_SHAPES, key=lambda r: 0 if r[3] == "row" else 1):
         n, k, o, kind = s
         if kind in ("column", "row"):
             n, k, o, kind = shard(s, world)
@@ -196,6 +197,37 @@ def cpu_pass(cases):
     return time.perf_counter() - t0, fl
 
 
+def bf16_linear_leg(rows, M, budget_s=8.0):
+    """model.py:155-157 on the host: weight_dequant once, then F.linear in bf16 with all the threads torch has.
+    Bounded: shapes are taken in order until the time budget is spent."""
+    import torch
+    import torch.nn.functional as F
+    torch.set_num_threads(max(1, len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)))
+    g = torch.Generator().manual_seed(1)
+    t_total, fl, used = 0.0, 0.0, []
+    for name, K, N, *_ in rows:
+        if N * K > (40 << 20):
+            continue                                           # keep the sample bounded: the three 117-132 MB weights are left out
+        w = (torch.randn(N, K, generator=g) * 0.02).to(torch.bfloat16)
+        x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+        F.linear(x, w)
+        reps, t0 = 0, time.perf_counter()
+        while reps < 3 or time.perf_counter() - t0 < 0.25:      # a quarter of a second per shape
+            F.linear(x, w)
+            reps += 1
+        t_total += time.perf_counter() - t0
+        fl += reps * gemm_flops(M, N, K)
+        used.append(name)
+        if t_total > budget_s:
+            break
+    return {"value": fl / t_total / 1e12 if t_total else None, "unit": "TFLOP/s", "threads": torch.get_num_threads(),
+            "cpu_count": os.cpu_count(), "sample": f"bf16 F.linear (model.py:155-157) at M={M} on {len(used)} shapes of the sweep "
+                                                   f"(weights up to 40 MB), repeated for 0.25 s each, {t_total:.2f} s"}
+
+
+REFERENCE_SAMPLE_M = 64
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -208,7 +240,7 @@ def run_reference(args):
     except AttributeError:
         O.set_num_threads(os.cpu_count() or 1)
     rows = sweep_rows(1)
-    M = 64
+    M = REFERENCE_SAMPLE_M
     cases = cpu_sample_inputs(rows, M)
     for _ in range(args.warmup):
         cpu_pass(cases)
@@ -218,13 +250,18 @@ def run_reference(args):
         t += dt
         fl += f
     val = fl / t / 1e12
-    sample = f"M=64 column of the sweep ({len(rows)} shapes), act_quant+fp8_gemm per shape"
+    sample = f"M={M} column of the sweep ({len(rows)} shapes), act_quant+fp8_gemm per shape"
+    cfg = workload_config(1)
+    cfg["workload"] = (f"bounded sample of BASELINE configs[1]: the M={M} column only ({len(rows)} (K->N) rows), act_quant + fp8_gemm "
+                       "per shape on the host; the GPU arm reports the same column as `same_sample_as_reference`")
+    cfg["m_values"] = [M]
     line = {
         "impl": "reference", "metric": "fp8_gemm_tflops_v3_shape_sweep", "value": val, "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t / args.steps * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 x fp8_e4m3 -> fp32",
-        "data": "synthetic", "config": workload_config(1),
-        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": O.num_threads(), "kind": "port", "sample": sample},
+        "data": "synthetic", "config": cfg,
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": O.num_threads(), "kind": "port", "sample": sample,
+                         "bf16_linear": bf16_linear_leg(rows, M)},
         "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
         "note": "reference = CPU restatement of inference/kernel.py (oracle/dsv3_oracle.c, OpenMP); the Python/Triton "
@@ -300,14 +337,34 @@ def run_ours(args):
     ref_flops = sum(gemm_flops(M, N, K) for M in MS for (_, K, N, *_r) in sweep_rows(1))
     assert abs(total_flops - ref_flops) <= 1e-9 * ref_flops, (total_flops, ref_flops)
 
-    def column(M):
-        """fp8_gemm for every shape of the sweep at one M (one CUDA graph per column)."""
+    comm = torch.cuda.Stream(device=dev) if world > 1 else None
+
+    def column(M, collectives=True, with_act_quant=False):
+        """fp8_gemm for every shape of the sweep at one M (one CUDA graph per column).  The all_reduce of a
+        row-parallel Linear (model.py:263-264) is issued on a communication stream as soon as its GEMM is done and
+        joins the main stream at the end of the column, so it runs under the GEMMs that follow."""
+        cur = torch.cuda.current_stream()
+        pending = []
         for name, K, N, _, ar, _c in rows:
-            _, xq, xs = acts[K]
+            x, xq, xs = acts[K]
             wq, ws = weights[name]
-            y = kernel.fp8_gemm(xq[:M], xs[:M], wq, ws)
-            if ar:
-                dist.all_reduce(y)
+            if with_act_quant:
+                xq_m, xs_m = kernel.act_quant(x[:M])
+                y = kernel.fp8_gemm(xq_m, xs_m, wq, ws)
+            else:
+                y = kernel.fp8_gemm(xq[:M], xs[:M], wq, ws)
+            if ar and collectives:
+                ev = torch.cuda.Event()
+                ev.record(cur)
+                comm.wait_event(ev)
+                with torch.cuda.stream(comm):
+                    dist.all_reduce(y)
+                y.record_stream(comm)
+                pending.append(y)
+        if pending:
+            ev = torch.cuda.Event()
+            ev.record(comm)
+            cur.wait_event(ev)
 
     def barrier():
         if world > 1:
@@ -319,44 +376,64 @@ def run_ours(args):
     # then runs the launches back to back.  Capture happens on the stream the warm-up ran on so the
     # split-K workspace of that stream already exists.
     side = torch.cuda.Stream(device=dev)
-    graphs = {}
+    graphs, graphs_nocomm, graphs_linear = {}, {}, {}
     with torch.cuda.stream(side):
         for _ in range(max(args.warmup, 3)):
             for M in MS:
                 column(M)
-        dsv3_b200.check_device_status()
         for M in MS:
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=side):
-                column(M)
-            graphs[M] = g
+            column(M, with_act_quant=True)
+        dsv3_b200.check_device_status()
+
+        def capture(**kw):
+            out = {}
+            for M in MS:
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    column(M, **kw)
+                out[M] = g
+            return out
+        graphs = capture()
+        graphs_linear = capture(with_act_quant=True)
+        if world > 1:
+            graphs_nocomm = capture(collectives=False)
         for M in MS:
             graphs[M].replay()
     barrier()
+
+    def timed_pass(gs, steps):
+        """Replays the eight column graphs `steps` times; returns (ms, per-step list of per-column event lists)."""
+        evs = []
+        barrier()
+        with torch.cuda.stream(side):
+            a = torch.cuda.Event(enable_timing=True); b = torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(steps):
+                marks = [torch.cuda.Event(enable_timing=True) for _ in range(len(MS) + 1)]
+                marks[0].record()
+                for i, M in enumerate(MS):          # M-major: every weight is used once per column
+                    gs[M].replay()
+                    marks[i + 1].record()
+                evs.append(marks)
+            b.record()
+        barrier()
+        t = a.elapsed_time(b)
+        if world > 1:
+            tt = torch.tensor([t], device=dev, dtype=torch.float64)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            t = tt.item()
+        return t, evs
 
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
     # ---- timed region 1: resident inputs ----------------------------------------------
-    col_events = []
-    barrier()
-    with torch.cuda.stream(side):
-        t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
-        t0.record()
-        for _ in range(args.steps):
-            marks = [torch.cuda.Event(enable_timing=True) for _ in range(len(MS) + 1)]
-            marks[0].record()
-            for i, M in enumerate(MS):          # M-major: every weight is used once per column
-                graphs[M].replay()
-                marks[i + 1].record()
-            col_events.append(marks)
-        t1.record()
-    barrier()
-    ms = t0.elapsed_time(t1)
-    if world > 1:
-        tt = torch.tensor([ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        ms = tt.item()
+    ms, col_events = timed_pass(graphs, args.steps)
+    dsv3_b200.check_device_status()
+    # the same sweep as the two-operator Linear of model.py:158-160 (act_quant + fp8_gemm), still device resident
+    ms_linear, _ = timed_pass(graphs_linear, args.steps)
+    # N > 1: the same GEMMs without the collectives, to tell compute from communication
+    ms_nocomm, nocomm_events = (timed_pass(graphs_nocomm, args.steps) if world > 1 else (None, None))
     dsv3_b200.check_device_status()
 
     # ---- timed region 2: end to end through the drop-in module, host buffers ----------
@@ -373,9 +450,9 @@ def run_ours(args):
     Kmax = max(acts)
     xbuf = [torch.empty(Mmax * Kmax, device=dev, dtype=torch.bfloat16) for _ in range(2)]
 
-    def e2e_step():
+    def e2e_step(items=None):
         done = [None, None]      # event: the GEMM that read xbuf[i] has finished
-        for i, (name, K, N, M, ar) in enumerate(plan):
+        for i, (name, K, N, M, ar) in enumerate(plan if items is None else items):
             wq, ws = weights[name]
             b = i & 1
             with torch.cuda.stream(s_in):
@@ -416,7 +493,66 @@ def run_ours(args):
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         ms_e2e = tt.item()
     dsv3_b200.check_device_status()
+    # the reference arm's sample (the M = 64 column), end to end, for a like-for-like ratio
+    sample_items = [it for it in plan if it[3] == REFERENCE_SAMPLE_M]
+    with torch.cuda.stream(side):
+        e2e_step(sample_items)
+    barrier()
+    q0 = torch.cuda.Event(enable_timing=True); q1 = torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(side):
+        q0.record()
+        for _ in range(args.steps):
+            e2e_step(sample_items)
+        q1.record()
+    barrier()
+    ms_e2e_sample = q0.elapsed_time(q1)
+    if world > 1:
+        tt = torch.tensor([ms_e2e_sample], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms_e2e_sample = tt.item()
     clocks = sampler.stop() if rank == 0 else None
+
+    # ---- per-shape table at the M values the targets are stated for (single GPU): every problem alone, a CUDA
+    # graph of launches over distinct copies of the weight (more than L2 in total)
+    per_shape = None
+    if world == 1 and not args.no_per_shape:
+        per_shape = []
+        fp8_pk = 2.0 * peaks["bf16_tflops"]
+        for name, K, N, *_r in rows:
+            wq0, ws0 = weights[name]
+            R = max(2, min(32, -(-(256 << 20) // (N * K))))
+            copies = [(wq0, ws0)] + [(wq0.clone(), ws0.clone()) for _ in range(R - 1)]
+            for M in (1, 64, 4096, 16384):
+                _, xq, xs = acts[K]
+                with torch.cuda.stream(side):
+                    for wq, ws in copies[:2]:
+                        kernel.fp8_gemm(xq[:M], xs[:M], wq, ws)
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=side):
+                        for wq, ws in copies:
+                            kernel.fp8_gemm(xq[:M], xs[:M], wq, ws)
+                    g.replay()
+                    a = torch.cuda.Event(enable_timing=True); b = torch.cuda.Event(enable_timing=True)
+                    a.record()
+                    g.replay(); g.replay()
+                    b.record()
+                torch.cuda.synchronize()
+                us = a.elapsed_time(b) * 1e3 / (2 * R)
+                t_c = gemm_flops(M, N, K) / (fp8_pk * 1e12) * 1e6
+                t_m = gemm_bytes(M, N, K) / (peaks["hbm_gbs"] * 1e9) * 1e6
+                bound = "tensor" if t_c > t_m else "hbm"
+                target = 0.70 if M >= 4096 else 0.75
+                entry = {"shape": name, "K": K, "N": N, "M": M, "us": round(us, 2), "bound": bound,
+                         "tflops": round(gemm_flops(M, N, K) / us / 1e6, 1), "gbs": round(gemm_bytes(M, N, K) / us / 1e3),
+                         "roofline_us": round(max(t_c, t_m), 2), "frac": round(max(t_c, t_m) / us, 3), "target": target}
+                if M <= 64 and max(t_c, t_m) < 2.5:
+                    # a launch costs about 2.5 us on this GPU whatever it does (the reference's own Triton launches measure
+                    # 2.6 us on its smallest problem): a roofline time below that cannot be met by any single launch
+                    entry["out_of_reach"] = "roofline time is below the cost of a launch"
+                per_shape.append(entry)
+                del g
+            del copies
+        dsv3_b200.check_device_status()
 
     # ---- per-kernel roofline from the per-column events of region 1 -------------------
     big_t = big_f = small_t = small_b = 0.0
@@ -433,7 +569,10 @@ def run_ours(args):
                 big_t += dt; big_f += fl; n_big += len(rows)
             elif M <= 64:
                 small_t += dt; small_b += by; n_small += len(rows)
-    fp8_peak = 2.0 * peaks["bf16_tflops_sustained"]
+    # FP8 issues at twice the bf16 rate.  The burst figure is the denominator: the timed region lasts a fraction of a
+    # second; the fraction of the sustained figure (a seconds-long cuBLAS loop under the power cap) is given beside it.
+    fp8_peak = 2.0 * peaks["bf16_tflops"]
+    fp8_sustained = 2.0 * peaks["bf16_tflops_sustained"]
     # DRAM traffic per launch: ncu's dram__bytes_read.sum + dram__bytes_write.sum of one captured launch
     # (bench.py --single, summaries under profiles/) divided by that problem's algorithmic bytes, applied
     # to the average algorithmic bytes of the launches timed here (traffic tracks the operand and result
@@ -442,25 +581,50 @@ def run_ours(args):
     small_avg = sum(gemm_bytes(M, N, K) for M in MS if M <= 64 for _, K, N, *_r in rows) / max(1, n_small // max(1, len(col_events)))
     ratio_big = NCU_TRAFFIC["token_major"][0] / gemm_bytes(*NCU_TRAFFIC["token_major"][1])
     ratio_small = NCU_TRAFFIC["weight_major"][0] / gemm_bytes(*NCU_TRAFFIC["weight_major"][1])
+    ach_big = big_f / big_t / 1e12 if big_t else None
     roofline = {
-        "kernel": "fp8_gemm_tc_kernel<128,false> (tcgen05, token-major tiles; launches with M >= 256)",
-        "bound": "tensor", "achieved": big_f / big_t / 1e12 if big_t else None, "peak": fp8_peak, "unit": "TFLOP/s",
-        "frac": (big_f / big_t / 1e12) / fp8_peak if big_t else None,
+        "kernel": "token-major tcgen05 kernels (launches with M >= 256): fp8_gemm_tm_kernel (CTA pairs, 256x128 tiles, K >= 1536) "
+                  "and fp8_gemm_tc_kernel<128,false> (short K, split-K)",
+        "bound": "tensor", "achieved": ach_big, "peak": fp8_peak, "unit": "TFLOP/s",
+        "frac": ach_big / fp8_peak if big_t else None,
+        "frac_of_sustained": ach_big / fp8_sustained if big_t else None,
         "traffic": ratio_big * big_b if n_big else None, "traffic_unit": "bytes per launch (average launch)",
         "traffic_source": f"{NCU_TRAFFIC['token_major'][2]}: measured / algorithmic bytes = {ratio_big:.2f}",
-        "peak_source": f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({peaks['source']}); FP8 issues at twice the bf16 rate",
+        "peak_source": f"2 x bf16_tflops (burst) of MEASURED_PEAKS.json ({peaks['source']}): the timed region is a fraction of a "
+                       f"second; frac_of_sustained uses 2 x bf16_tflops_sustained = {fp8_sustained:.0f}",
         "launches": n_big, "avg_launch_us": big_t / n_big * 1e6 if n_big else None,
         "algorithmic": "2*M*N*K flops per launch",
+        "includes_collectives": world > 1,
     }
     roofline_decode = {
-        "kernel": "fp8_gemm_tc_kernel<BN,true> (tcgen05, weight-major tiles, split-K; launches with M <= 64)",
+        "kernel": "decode launches (M <= 64): fp8_gemm_tc_kernel<BN,true> (tcgen05, weight-major tiles, split-K) and "
+                  "fp8_linear_small_kernel (M <= 8, small weights)",
         "bound": "hbm", "achieved": small_b / small_t / 1e9 if small_t else None, "peak": peaks["hbm_gbs"], "unit": "GB/s",
         "frac": (small_b / small_t / 1e9) / peaks["hbm_gbs"] if small_t else None,
         "traffic": ratio_small * small_avg if n_small else None, "traffic_unit": "bytes per launch (average launch)",
         "traffic_source": f"{NCU_TRAFFIC['weight_major'][2]}: measured / algorithmic bytes = {ratio_small:.2f}",
         "peak_source": f"hbm_gbs of MEASURED_PEAKS.json ({peaks['source']})",
         "launches": n_small, "algorithmic": "M*K + N*K + scales + 2*M*N bytes per launch",
+        "includes_collectives": world > 1,
     }
+    # N > 1: compute (the same graphs without collectives) against the full step, per column
+    breakdown = None
+    if world > 1:
+        comp = {M: 0.0 for M in MS}
+        for marks in nocomm_events:
+            for i, M in enumerate(MS):
+                comp[M] += marks[i].elapsed_time(marks[i + 1])
+        full = {M: per_column[M][0] * 1e3 for M in MS}
+        n = len(nocomm_events)
+        breakdown = {
+            "compute_ms_per_step": ms_nocomm / args.steps, "comm_exposed_ms_per_step": (ms - ms_nocomm) / args.steps,
+            "per_column": {f"M={M}": {"compute_ms": comp[M] / n, "step_ms": full[M] / len(col_events),
+                                      "comm_exposed_ms": full[M] / len(col_events) - comp[M] / n} for M in MS},
+            "note": "rank 0's device times; compute = the same CUDA graphs captured without the all_reduce calls; the "
+                    "all_reduce of a row-parallel Linear runs on a communication stream under the following GEMMs",
+        }
+        roofline["achieved_compute_only"] = (sum(gemm_flops(M, N, K) for M in MS if M >= 256 for _, K, N, *_r in rows) /
+                                             (sum(comp[M] for M in MS if M >= 256) / n * 1e-3) / 1e12)
     detail = {f"M={k}": {"us_per_column": v[0] / v[1] * 1e6, "tflops": v[2] / (v[0] / v[1]) / 1e12,
                          "gbs": v[3] / (v[0] / v[1]) / 1e9, "launches": len(rows)} for k, v in per_column.items()}
 
@@ -473,6 +637,8 @@ def run_ours(args):
         killer.daemon = True
         killer.start()
         graphs.clear()
+        graphs_nocomm.clear()
+        graphs_linear.clear()
         torch.cuda.synchronize()
         dist.barrier()
         dist.destroy_process_group()
@@ -489,7 +655,8 @@ def run_ours(args):
         cases = cpu_sample_inputs(sweep_rows(1), 64)
         dt, fl = cpu_pass(cases)
         cpu = {"value": fl / dt / 1e12, "unit": "TFLOP/s", "cores": O.num_threads(), "kind": "port",
-               "sample": f"M=64 column of the sweep ({len(cases)} shapes), act_quant+fp8_gemm per shape, one pass, {dt:.1f} s"}
+               "sample": f"M=64 column of the sweep ({len(cases)} shapes), act_quant+fp8_gemm per shape, one pass, {dt:.1f} s",
+               "bf16_linear": bf16_linear_leg(sweep_rows(1), REFERENCE_SAMPLE_M)}
 
     agg = total_flops * args.steps / (ms * 1e-3) / 1e12
     agg_e2e = total_flops * args.steps / (ms_e2e * 1e-3) / 1e12
@@ -505,6 +672,16 @@ def run_ours(args):
                         "weights resident on the device; upload, compute and download on three streams"},
         "gpu_launches": len(plan) * args.steps, "gpu_launches_e2e": 2 * len(plan) * args.steps,
         "clocks": clocks, "per_column": detail,
+        # the two-operator Linear of model.py:158-160 (act_quant + fp8_gemm per problem), device resident
+        "value_act_quant_plus_gemm": total_flops * args.steps / (ms_linear * 1e-3) / 1e12,
+        # the sample the reference arm times (its config.workload): the M = 64 column
+        "same_sample_as_reference": {
+            "workload": f"M={REFERENCE_SAMPLE_M} column of the sweep",
+            "value": per_column[REFERENCE_SAMPLE_M][2] / (per_column[REFERENCE_SAMPLE_M][0] / per_column[REFERENCE_SAMPLE_M][1]) / 1e12,
+            "e2e": (sum(gemm_flops(M, N, K) for _, K, N, M, _ in sample_items) * args.steps / (ms_e2e_sample * 1e-3) / 1e12
+                    if world == 1 else None),
+            "unit": "TFLOP/s"},
+        "comm_breakdown": breakdown, "per_shape": per_shape,
     }
     sys.stdout.flush()
     os.dup2(saved_stdout, 1)
@@ -759,6 +936,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-per-shape", action="store_true", help="skip the per-shape table of the default run")
     ap.add_argument("--single", default=None, metavar="M,N,K",
                     help="run one problem instead of the sweep (the case ncu captures are taken on)")
     ap.add_argument("--detail", action="store_true", help="per-(shape, M) table instead of the aggregate sweep")

@@ -390,7 +390,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
         const int64_t M = p.M, N = p.N;
         const int kc = p.kc;
         uint32_t g = 0;          // unit counter at the start of the current item
-        uint32_t item_no = 0;    // items done by this CTA (phase of the scale-table barriers, ticket slot)
+        uint32_t item_no = 0;    // non-empty items done by this CTA (phase of the scale-table barriers, ticket slot)
         bool ok = true;
 
         // A chunk is read back in SPC steps of HC columns so that one step's TMEM load is in flight
@@ -425,8 +425,11 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
             }
         };
 
-        for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x, ++item_no) {
+        for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
             const Item it = decode_item<BN, kSwap>(item, p, g_prefix);
+            // grouped mode: slots beyond the last token tile carry no work; they cost a decode and nothing else
+            if (it.c1 <= it.c0) continue;
+            const uint32_t item_cur = item_no++;
             float2 acc[CPT / 2];
 #pragma unroll
             for (int j = 0; j < CPT / 2; ++j) acc[j] = make_float2(0.0f, 0.0f);
@@ -452,7 +455,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
             // item never has more chunks than the table holds.)
             if constexpr (kSwap) {
                 {
-                    bool mine = bounded_wait(tab_free_bar, (item_no & 1u) ^ 1u, ctl, p.status, 7, item_no);
+                    bool mine = bounded_wait(tab_free_bar, (item_cur & 1u) ^ 1u, ctl, p.status, 7, item_cur);
                     ok = __all_sync(0xffffffffu, mine);
                     if (!ok) break;
                     const int tid = threadIdx.x - kFirstPromoWarp * 32;
@@ -462,7 +465,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
                         sc_tab[idx] = __ldg(as_ptr + m * kc + it.c0 + chl) * __ldg(bs_ptr + it.c0 + chl);
                     }
                     mbar_arrive(tab_ready_bar);
-                    mine = bounded_wait(tab_ready_bar, item_no & 1u, ctl, p.status, 8, item_no);
+                    mine = bounded_wait(tab_ready_bar, item_cur & 1u, ctl, p.status, 8, item_cur);
                     ok = __all_sync(0xffffffffu, mine);
                     if (!ok) break;
                 }
@@ -623,7 +626,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
                 // Release: the barrier orders every writer's stores before the ticket thread's fence, which
                 // is cumulative.  The ticket slot alternates between items, so the next item's ticket cannot
                 // overwrite this one before every thread has read it (a barrier of the next item lies between).
-                const int slot = static_cast<int>(item_no & 1u);
+                const int slot = static_cast<int>(item_cur & 1u);
                 promo_barrier<kWriters>();
                 if (threadIdx.x == kFirstPromoWarp * 32) {
                     // one acquire-release atomic: releases the partial tiles (cumulative over the barrier above) and
@@ -1037,7 +1040,7 @@ int build_group_table(void* table_dev, const void* const* weights, const float* 
 }
 
 int launch_fp8_gemm_grouped(const void* table_dev, int n, const void* a, const float* a_s, const int* seg_dev,
-                            int64_t rows_total, int64_t N, int64_t K, void* c, cudaStream_t stream) {
+                            int64_t rows_total, int64_t rows_hint, int64_t N, int64_t K, void* c, cudaStream_t stream) {
     if (rows_total <= 0 || N <= 0) return DSV3_OK;
     if (!tc_supported(a, a, c, rows_total, N, K) || n <= 0 || n > kMaxGroups) {
         set_last_error("grouped fp8_gemm: needs K %% 16 == 0, 16-byte aligned a and c, and 1..%d groups", kMaxGroups);
@@ -1049,7 +1052,9 @@ int launch_fp8_gemm_grouped(const void* table_dev, int n, const void* a, const f
                        static_cast<long long>(K), scale_tab_chunks(32) * kChunk);
         return DSV3_ERR_UNSUPPORTED;
     }
-    const int64_t avg = (rows_total + n - 1) / n;          // the counts themselves live on the device
+    // the counts themselves live on the device: the token tile is sized for the expected load per group
+    const int64_t expect = (rows_hint > 0 && rows_hint < rows_total) ? rows_hint : rows_total;
+    const int64_t avg = (expect + n - 1) / n;
     int bn = avg <= 16 ? 16 : (avg <= 32 ? 32 : 64);
     if (kc > scale_tab_chunks(bn)) bn = 32;                // the 64-token variant's table is shorter
     CUtensorMap tq, dummy;

@@ -47,7 +47,7 @@ size_t group_table_bytes(int n);
 int build_group_table(void* table_dev, const void* const* weights, const float* const* scales, int n, int64_t N,
                       int64_t K, cudaStream_t stream);
 int launch_fp8_gemm_grouped(const void* table_dev, int n, const void* a, const float* a_s, const int* seg_dev,
-                            int64_t rows_total, int64_t N, int64_t K, void* c, cudaStream_t stream);
+                            int64_t rows_total, int64_t rows_hint, int64_t N, int64_t K, void* c, cudaStream_t stream);
 
 // Kernel / split-K override set through dsv3_set_gemm_policy (0 = automatic).
 int gemm_policy_kernel();

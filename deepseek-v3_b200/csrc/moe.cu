@@ -137,8 +137,8 @@ int dsv3_group_table_build(void* table, const void* const* weights, const float*
 }
 
 int dsv3_fp8_gemm_grouped(const void* table, int n_groups, const void* a, const float* a_s, const int32_t* seg,
-                          int64_t rows_total, int64_t N, int64_t K, void* c, dsv3_stream_t stream) {
-    if (rows_total < 0 || N < 0 || K <= 0) {
+                          int64_t rows_total, int64_t rows_hint, int64_t N, int64_t K, void* c, dsv3_stream_t stream) {
+    if (rows_total < 0 || rows_hint < 0 || N < 0 || K <= 0) {
         set_last_error("fp8_gemm_grouped: negative size");
         return DSV3_ERR_INVALID_ARGUMENT;
     }
@@ -147,7 +147,8 @@ int dsv3_fp8_gemm_grouped(const void* table, int n_groups, const void* a, const 
         set_last_error("fp8_gemm_grouped: null pointer");
         return DSV3_ERR_INVALID_ARGUMENT;
     }
-    return launch_fp8_gemm_grouped(table, n_groups, a, a_s, seg, rows_total, N, K, c, static_cast<cudaStream_t>(stream));
+    return launch_fp8_gemm_grouped(table, n_groups, a, a_s, seg, rows_total, rows_hint, N, K, c,
+                                   static_cast<cudaStream_t>(stream));
 }
 
 int dsv3_moe_route(const int64_t* indices, const float* weights, int64_t T, int topk, int start, int n_local,

@@ -60,7 +60,7 @@ def _load() -> ctypes.CDLL:
     lib.dsv3_group_table_bytes.restype = sz
     lib.dsv3_group_table_build.argtypes = [vp, vp, vp, ci, i64, i64, vp]
     lib.dsv3_group_table_build.restype = ci
-    lib.dsv3_fp8_gemm_grouped.argtypes = [vp, ci, vp, vp, vp, i64, i64, i64, vp, vp]
+    lib.dsv3_fp8_gemm_grouped.argtypes = [vp, ci, vp, vp, vp, i64, i64, i64, i64, vp, vp]
     lib.dsv3_fp8_gemm_grouped.restype = ci
     lib.dsv3_moe_combine.argtypes = [vp, vp, vp, i64, ci, i64, vp, vp]
     lib.dsv3_moe_combine.restype = ci

@@ -51,19 +51,21 @@ class GroupedExperts:
             self.tables[name] = (table, N, K)
         self.signature = tuple(getattr(e, n).weight.data_ptr() for e in experts for n in ("w1", "w2", "w3"))
 
-    def gemm(self, name: str, a: torch.Tensor, a_s: torch.Tensor, seg: torch.Tensor) -> torch.Tensor:
+    def gemm(self, name: str, a: torch.Tensor, a_s: torch.Tensor, seg: torch.Tensor, rows_hint: int = 0) -> torch.Tensor:
         table, N, K = self.tables[name]
         rows = a.size(0)
         c = torch.empty(rows, N, dtype=torch.bfloat16, device=a.device)
         _lib.check(lib.dsv3_fp8_gemm_grouped(table.data_ptr(), self.n, a.data_ptr(), a_s.data_ptr(), seg.data_ptr(),
-                                             rows, N, K, c.data_ptr(), _stream()))
+                                             rows, rows_hint, N, K, c.data_ptr(), _stream()))
         return c
 
-    def routed(self, x: torch.Tensor, weights: torch.Tensor, indices: torch.Tensor) -> torch.Tensor:
-        """Sum over the local experts of ``expert(x[idx]) * weights`` (model.py:683-689)."""
+    def routed(self, x: torch.Tensor, weights: torch.Tensor, indices: torch.Tensor, n_routed: int = 0) -> torch.Tensor:
+        """Sum over the local experts of ``expert(x[idx]) * weights`` (model.py:683-689).  ``n_routed``: experts of
+        the whole layer (this rank owns ``self.n`` of them and, on average, that share of the pairs)."""
         T, topk = indices.shape
         P = T * topk
         n = self.n
+        hint = max(1, (P * n + n_routed - 1) // n_routed) if n_routed > n else 0
         with torch.cuda.device(x.device):
             # ---- group the (token, expert) pairs by local expert (pairs of other ranks' experts go last) and
             # order every token's pairs by expert id: one launch, nothing read back
@@ -82,9 +84,9 @@ class GroupedExperts:
             xq_p = xq.view(torch.uint8).index_select(0, tok).view(torch.float8_e4m3fn)
             xs_p = xs.index_select(0, tok)
             # ---- w2(silu(w1 x) * w3 x), the bf16 rounding points of Expert.forward (model.py:633)
-            h = F.silu(self.gemm("w1", xq_p, xs_p, seg)) * self.gemm("w3", xq_p, xs_p, seg)
+            h = F.silu(self.gemm("w1", xq_p, xs_p, seg, hint)) * self.gemm("w3", xq_p, xs_p, seg, hint)
             hq, hs = act_quant(h, 128, self.scale_fmt)
-            o = self.gemm("w2", hq, hs, seg)
+            o = self.gemm("w2", hq, hs, seg, hint)
             # ---- y[t] = sum over the token's local experts, ascending expert id, bf16 at every step
             y = torch.empty(T, self.dim, dtype=torch.bfloat16, device=x.device)
             _lib.check(lib.dsv3_moe_combine(o.data_ptr(), pos_s.data_ptr(), w_s.data_ptr(), T, topk, self.dim,
@@ -112,7 +114,7 @@ def grouped_moe_forward(self, x: torch.Tensor, *, world_size: int = 1, fallback=
     shape = x.size()
     x = x.view(-1, self.dim)
     weights, indices = self.gate(x)
-    y = _grouped(self).routed(x, weights, indices)
+    y = _grouped(self).routed(x, weights, indices, getattr(self, "n_routed_experts", 0))
     z = self.shared_experts(x)
     if world_size > 1:
         import torch.distributed as dist

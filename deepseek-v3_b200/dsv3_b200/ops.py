@@ -82,6 +82,38 @@ def act_quant(x: torch.Tensor, block_size: int = 128, scale_fmt: Optional[str] =
     return y, s
 
 
+# Cache of de-quantised weights (off by default).  MLA.forward in "absorb" mode de-quantises wkv_b on every call of
+# every layer (model.py:481) although the weight never changes; with the cache on, the call after the first returns
+# the tensor computed before and launches nothing.  An entry is keyed on the weight's and the scales' storage
+# address, shape and in-place modification counter and holds a weak reference to the weight, so loading new values
+# into the parameter (copy_, load_model) or freeing it invalidates the entry.
+_dequant_cache = None            # OrderedDict when enabled
+_dequant_cache_limit = 0
+dequant_stats = {"launches": 0, "hits": 0}
+
+
+def enable_weight_dequant_cache(max_bytes: int = 2 << 30) -> None:
+    """Remember the results of ``weight_dequant`` (up to ``max_bytes`` of bf16 copies, oldest dropped first).
+    The caller must treat the returned tensors as read-only (model.py:481-495 only views and multiplies them).
+    Meant for inference loops; leave it off for one-pass tools such as ``fp8_cast_bf16.py``."""
+    global _dequant_cache, _dequant_cache_limit
+    import collections
+    _dequant_cache = collections.OrderedDict()
+    _dequant_cache_limit = int(max_bytes)
+
+
+def disable_weight_dequant_cache() -> None:
+    global _dequant_cache
+    _dequant_cache = None
+
+
+def _version_or_none(t: torch.Tensor):
+    try:
+        return t._version
+    except RuntimeError:          # inference tensors carry no counter: never cached
+        return None
+
+
 def weight_dequant(x: torch.Tensor, s: torch.Tensor, block_size: int = 128) -> torch.Tensor:
     """De-quantise a block-scaled FP8 weight to the default dtype (kernel.py:89-110)."""
     assert x.is_contiguous() and s.is_contiguous(), 'Input tensors must be contiguous'
@@ -90,9 +122,30 @@ def weight_dequant(x: torch.Tensor, s: torch.Tensor, block_size: int = 128) -> t
     if x.element_size() != 1 or s.dtype != torch.float32:
         raise NotImplementedError("weight_dequant takes a 1-byte FP8 weight and float32 scales")
     M, N = x.size()
+    key = None
+    if _dequant_cache is not None:
+        vx, vs = _version_or_none(x), _version_or_none(s)
+        if vx is not None and vs is not None:
+            key = (x.data_ptr(), s.data_ptr(), M, N, block_size, vx, vs, _out_dtype())
+            hit = _dequant_cache.get(key)
+            if hit is not None and hit[0]() is x:
+                _dequant_cache.move_to_end(key)
+                dequant_stats["hits"] += 1
+                return hit[1]
     y = torch.empty_like(x, dtype=_out_dtype())
     with torch.cuda.device(dev):
         _lib.check(lib.dsv3_weight_dequant(x.data_ptr(), s.data_ptr(), M, N, block_size, y.data_ptr(), _stream()))
+    dequant_stats["launches"] += 1
+    if key is not None:
+        import weakref
+        try:
+            _dequant_cache[key] = (weakref.ref(x), y)
+        except TypeError:
+            return y
+        total = sum(v[1].numel() * v[1].element_size() for v in _dequant_cache.values())
+        while total > _dequant_cache_limit and len(_dequant_cache) > 1:
+            _, old = _dequant_cache.popitem(last=False)
+            total -= old[1].numel() * old[1].element_size()
     return y
 
 

@@ -145,6 +145,9 @@ int dsv3_set_gemm_policy(int kernel, int split_k);
  *              sorted by expert
  *   seg      : int32 [n + 1] in DEVICE memory: expert e owns rows [seg[e], seg[e+1]); rows at and
  *              beyond seg[n] are ignored.  Nothing is read back to the host.
+ *   rows_hint: how many rows the n groups are expected to own together (seg[n] itself stays on the device), or 0
+ *              if unknown (then rows_total).  Only a tuning input: it picks the token-tile width.  With tensor
+ *              parallelism a rank owns n of the E experts and about rows_total * n / E of the rows.
  *   c        : bf16 [rows_total, N]; row r = a[r] @ weight[e(r)]^T with the block scales applied.
  * Limits: n <= 256, K <= 18432, K % 16 == 0.
  */
@@ -152,7 +155,7 @@ size_t dsv3_group_table_bytes(int n_groups);
 int dsv3_group_table_build(void* table, const void* const* weights, const float* const* scales, int n_groups,
                            int64_t N, int64_t K, dsv3_stream_t stream);
 int dsv3_fp8_gemm_grouped(const void* table, int n_groups, const void* a, const float* a_s, const int32_t* seg,
-                          int64_t rows_total, int64_t N, int64_t K, void* c, dsv3_stream_t stream);
+                          int64_t rows_total, int64_t rows_hint, int64_t N, int64_t K, void* c, dsv3_stream_t stream);
 
 /*
  * Routing bookkeeping of the expert loop in one launch -- replaces `counts = torch.bincount(indices.flatten())`

@@ -190,7 +190,7 @@ def _grouped(lib, _lib, weights, a_q, a_s, seg, N, K):
     _lib.check(lib.dsv3_group_table_build(table.data_ptr(), wp, sp, n, N, K, st))
     rows = a_q.size(0)
     c = torch.full((rows, N), float("nan"), dtype=torch.bfloat16, device="cuda")
-    _lib.check(lib.dsv3_fp8_gemm_grouped(table.data_ptr(), n, a_q.data_ptr(), a_s.data_ptr(), seg.data_ptr(), rows, N, K,
+    _lib.check(lib.dsv3_fp8_gemm_grouped(table.data_ptr(), n, a_q.data_ptr(), a_s.data_ptr(), seg.data_ptr(), rows, 0, N, K,
                                          c.data_ptr(), st))
     torch.cuda.synchronize()
     return c

@@ -150,3 +150,43 @@ def test_weight_quant_bit_exact_vs_oracle(N, Kd, seed):
     q, s = dsv3_b200.weight_quant(w.cuda())
     qo, so = O.weight_quant(w)
     assert np.array_equal(f32_bits(s), f32_bits(so)) and np.array_equal(u8(q), u8(qo))
+
+
+def test_weight_dequant_cache_skips_the_launch_for_an_unchanged_weight():
+    """model.py:481 de-quantises wkv_b on every forward of every layer; with the cache on, only the first call launches.
+    The cache must notice new values in the parameter and must not outlive it."""
+    import dsv3_b200
+    import kernel
+    from dsv3_b200 import ops
+    torch.set_default_dtype(torch.bfloat16)
+    try:
+        _, _, wq, ws = O.make_case(1, 4096, 512, 13)               # wkv_b at TP=8
+        wq, ws = wq.cuda(), ws.cuda()
+        ref = O.weight_dequant(wq.cpu(), ws.cpu())
+        dsv3_b200.enable_weight_dequant_cache(64 << 20)
+        ops.dequant_stats.update(launches=0, hits=0)
+        y1 = kernel.weight_dequant(wq, ws)
+        y2 = kernel.weight_dequant(wq, ws)
+        assert y2 is y1 and ops.dequant_stats == {"launches": 1, "hits": 1}
+        assert np.array_equal(bf16_bits(y1), bf16_bits(ref))
+        # new values loaded into the same storage (what load_model does): recomputed
+        wq.view(torch.uint8).copy_(torch.flip(wq.view(torch.uint8), dims=[0]))
+        y3 = kernel.weight_dequant(wq, ws)
+        assert ops.dequant_stats["launches"] == 2
+        assert np.array_equal(bf16_bits(y3), bf16_bits(O.weight_dequant(wq.cpu(), ws.cpu())))
+        # a different weight object is a different entry, even at a recycled address
+        wq2 = wq.clone()
+        kernel.weight_dequant(wq2, ws)
+        assert ops.dequant_stats["launches"] == 3
+        # inference-mode tensors have no modification counter: never cached
+        with torch.inference_mode():
+            wi = wq.clone()
+            kernel.weight_dequant(wi, ws); kernel.weight_dequant(wi, ws)
+        assert ops.dequant_stats["launches"] == 5
+        # off again: every call launches
+        dsv3_b200.disable_weight_dequant_cache()
+        kernel.weight_dequant(wq, ws); kernel.weight_dequant(wq, ws)
+        assert ops.dequant_stats["launches"] == 7
+    finally:
+        dsv3_b200.disable_weight_dequant_cache()
+        torch.set_default_dtype(torch.float32)
