@@ -25,7 +25,8 @@ EXPORTS = (
     "dsv3_fp8_gemm_workspace_bytes", "dsv3_fp8_gemm", "dsv3_set_gemm_policy", "dsv3_weight_quant",
     "dsv3_check_device_status", "dsv3_fp8_gemm_static", "dsv3_fp8_gemm_static_scratch_bytes",
     "dsv3_group_table_bytes", "dsv3_group_table_build", "dsv3_fp8_gemm_grouped", "dsv3_moe_combine", "dsv3_moe_route",
-    "dsv3_fp8_linear",
+    "dsv3_fp8_linear", "dsv3_p2p_handle_bytes", "dsv3_p2p_create", "dsv3_p2p_connect", "dsv3_p2p_connect_local", "dsv3_p2p_base",
+    "dsv3_allreduce_oneshot", "dsv3_allreduce_oneshot_pair_on_one_gpu", "dsv3_p2p_destroy",
 )
 
 
@@ -51,6 +52,16 @@ def _load() -> ctypes.CDLL:
     lib.dsv3_fp8_gemm_workspace_bytes.argtypes = [i64, i64, i64]
     lib.dsv3_fp8_gemm_workspace_bytes.restype = sz
     lib.dsv3_fp8_gemm.argtypes = [vp, vp, vp, vp, i64, i64, i64, vp, vp, sz, vp]
+    u64 = ctypes.c_uint64
+    lib.dsv3_p2p_handle_bytes.restype = sz
+    lib.dsv3_p2p_create.argtypes = [ci, ci, sz, ctypes.POINTER(vp), vp]
+    lib.dsv3_p2p_connect.argtypes = [vp, vp]
+    lib.dsv3_p2p_connect_local.argtypes = [vp, vp]
+    lib.dsv3_p2p_base.argtypes = [vp]
+    lib.dsv3_p2p_base.restype = vp
+    lib.dsv3_allreduce_oneshot.argtypes = [vp, vp, vp, i64, u64, vp]
+    lib.dsv3_allreduce_oneshot_pair_on_one_gpu.argtypes = [vp, vp, vp, vp, vp, vp, i64, u64, vp]
+    lib.dsv3_p2p_destroy.argtypes = [vp]
     lib.dsv3_fp8_linear.argtypes = [vp, i64, i64, vp, vp, i64, ci, vp, vp]
     lib.dsv3_fp8_linear.restype = ci
     lib.dsv3_fp8_gemm_static.argtypes = [vp, vp, vp, vp, i64, i64, i64, vp, vp]

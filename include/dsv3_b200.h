@@ -186,6 +186,35 @@ int dsv3_moe_combine(const void* o, const int32_t* pos, const void* w, int64_t T
                      dsv3_stream_t stream);
 
 /*
+ * One-shot all-reduce of a decode-sized bf16 tensor over peer-mapped buffers -- replaces `dist.all_reduce(y)` after
+ * a row-parallel Linear and after the MoE expert loop (model.py:263-264, 691-692) for small y, where a ring or tree
+ * collective is bound by latency.  One process per GPU; every rank
+ *   1. dsv3_p2p_create(rank, world, max_bytes, &comm, handle): allocates (cudaMalloc, once) this rank's exported
+ *      buffer and returns an inter-process handle of dsv3_p2p_handle_bytes() bytes;
+ *   2. exchanges the handles with all ranks by any host channel (torch.distributed.all_gather_object, a file, ...);
+ *   3. dsv3_p2p_connect(comm, handles): maps the peers' buffers (handles: world entries in rank order);
+ *   4. per all-reduce: dsv3_allreduce_oneshot(comm, in, out, count, limit_ns, stream) on every rank, in the same
+ *      order with the same count.  in: this rank's partial sums, out: the sum over ranks (may be the same pointer),
+ *      both bf16 [count], 16-byte aligned, count * 2 <= max_bytes.  Sums are formed in fp32 in rank order, so all
+ *      ranks obtain the same bits.  The call enqueues one kernel and returns; it may be captured in a CUDA graph.
+ * Peer memory is read with ordinary loads; nothing is multicast.  Every device-side wait is bounded by limit_ns
+ * (0 = one second): a rank that does not hear from a peer records the fact in the device status words
+ * (dsv3_check_device_status returns DSV3_ERR_DEVICE_TIMEOUT) and leaves `out` unwritten.  All ranks must destroy
+ * their communicators (dsv3_p2p_destroy) only after every rank's last all-reduce has completed.
+ * dsv3_p2p_connect_local / dsv3_p2p_base / dsv3_allreduce_oneshot_pair_on_one_gpu serve tests that play two ranks
+ * inside one process on one GPU: the two ranks' CTAs wait for each other, so they run as ONE cooperative launch.
+ */
+size_t dsv3_p2p_handle_bytes(void);
+int dsv3_p2p_create(int rank, int world, size_t max_bytes, void** comm_out, void* handle_out);
+int dsv3_p2p_connect(void* comm, const void* handles);
+int dsv3_p2p_connect_local(void* comm, void* const* bases);
+void* dsv3_p2p_base(void* comm);
+int dsv3_allreduce_oneshot(void* comm, const void* in, void* out, int64_t count, uint64_t limit_ns, dsv3_stream_t stream);
+int dsv3_allreduce_oneshot_pair_on_one_gpu(void* comm0, void* comm1, const void* in0, const void* in1, void* out0, void* out1,
+                                           int64_t count, uint64_t limit_ns, dsv3_stream_t stream);
+int dsv3_p2p_destroy(void* comm);
+
+/*
  * Harness weight quantiser (the reference ships only the inverse, weight_dequant;
  * the checkpoint format is described in README_WEIGHTS.md:60-92).
  *   w : bf16 [N, K] -> q : e4m3 [N, K], s : fp32 [ceil(N/128), ceil(K/128)]
