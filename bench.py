@@ -929,6 +929,227 @@ def run_moe_layer(args):
         killer.cancel()
 
 
+def run_decode_step(args):
+    """BASELINE configs[4] on the GEMM path: one decode step of the 671B-shaped model at tensor parallelism = world.
+
+    Per layer the Linear sequence of model.py at M = batch rows: MLA wq_a, wq_b, wkv_a, weight_dequant(wkv_b), wo
+    (+ all_reduce) (model.py:461-496); layers 0-2 the dense MLP w1, w3, w2 (+ all_reduce) (model.py:500-532); layers
+    3-60 the MoE layer: gate, routed experts of this rank (256 / world), shared expert (+ all_reduce), all_reduce
+    (model.py:669-693).  Attention scores, RoPE, norms, embedding and the bf16 head are outside the path and not
+    executed, so the figure is the time of the FP8 GEMM path of a step, not of the whole model.  Weights: random-init,
+    block-quantised; a few distinct instances of each layer kind (each larger than L2) are visited in rotation, which
+    keeps weights out of L2 between two uses without holding 85 GB per rank.
+    Modes: `operators` = the reference's call structure on the drop-in operators (act_quant + fp8_gemm per Linear,
+    Python expert loop with its host synchronisations); `seams` = linear seam (fused decode Linear), grouped MoE,
+    weight_dequant cache; `graph` = the seams step captured once in a CUDA graph and replayed."""
+    import torch
+    import torch.distributed as dist
+    import torch.nn.functional as F
+    import dsv3_b200
+    import kernel
+    from dsv3_b200 import linear_seam as L
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    sys.stdout.flush()
+    saved_stdout = os.dup(1)
+    os.dup2(2, 1)
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    torch.set_default_dtype(torch.bfloat16)
+    peaks = read_peaks()
+    dim, q_lora, kv_lora, rope, heads, nope, vdim = 7168, 1536, 512, 64, 128, 128, 128
+    inter, moe_inter, E, topk, n_groups, topk_groups, route_scale = 18432, 2048, 256, 8, 8, 4, 2.5
+    n_layers, n_dense = 61, 3
+    n_local = E // world
+    start = rank * n_local
+    gen = torch.Generator(device=dev).manual_seed(4000 + rank)
+
+    class Lin:
+        scale_fmt = None
+
+        def __init__(self, N, K):
+            w = (torch.randn(N, K, device=dev, dtype=torch.float32, generator=gen) * 0.02).to(torch.bfloat16)
+            self.weight, sc = dsv3_b200.weight_quant(w)
+            self.weight.scale = sc
+            self.bytes = N * K
+
+    class Expert:
+        def __init__(self, d, i):
+            self.w1, self.w2, self.w3 = Lin(i, d), Lin(d, i), Lin(i, d)
+
+    class Attn:
+        def __init__(self):
+            self.wq_a, self.wq_b = Lin(q_lora, dim), Lin(heads * (nope + rope) // world, q_lora)
+            self.wkv_a, self.wkv_b = Lin(kv_lora + rope, dim), Lin(heads * (nope + vdim) // world, kv_lora)
+            self.wo = Lin(dim, heads * vdim // world)
+            self.bytes = sum(l.bytes for l in (self.wq_a, self.wq_b, self.wkv_a, self.wkv_b, self.wo))
+
+    class Dense:
+        def __init__(self):
+            self.w1, self.w3, self.w2 = Lin(inter // world, dim), Lin(inter // world, dim), Lin(dim, inter // world)
+            self.bytes = 3 * self.w1.bytes
+
+    class MoE:
+        def __init__(self):
+            self.dim, self.n_routed_experts, self.n_local_experts, self.n_activated_experts = dim, E, n_local, topk
+            self.experts_start_idx, self.experts_end_idx = start, start + n_local
+            self.experts = [Expert(dim, moe_inter) if start <= i < start + n_local else None for i in range(E)]
+            self.shared = Expert(dim, moe_inter // world)
+            g2 = torch.Generator(device=dev).manual_seed(77)          # the gate is replicated: same on every rank
+            self.gate_w = (torch.randn(E, dim, device=dev, dtype=torch.float32, generator=g2) * 0.02).to(torch.bfloat16)
+            self.gate_b = torch.randn(E, device=dev, dtype=torch.float32, generator=g2) * 0.01
+
+        def gate(self, x):                                            # Gate.forward, model.py:566-598
+            scores = F.linear(x, self.gate_w).sigmoid()
+            original = scores
+            sc = (scores + self.gate_b).view(x.size(0), n_groups, -1)
+            group_scores = sc.topk(2, dim=-1)[0].sum(dim=-1)
+            idx = group_scores.topk(topk_groups, dim=-1)[1]
+            mask = sc.new_ones(x.size(0), n_groups, dtype=torch.bool).scatter_(1, idx, False)
+            sc = sc.masked_fill(mask.unsqueeze(-1), float("-inf")).flatten(1)
+            indices = torch.topk(sc, topk, dim=-1)[1]
+            weights = original.gather(1, indices)
+            weights = weights / weights.sum(dim=-1, keepdim=True) * route_scale
+            return weights.type_as(x), indices
+
+    n_inst = max(2, args.decode_instances)
+    attn = [Attn() for _ in range(n_inst)]
+    dense = [Dense() for _ in range(min(n_inst, n_dense))]
+    moes = [MoE() for _ in range(n_inst)]
+    torch.cuda.synchronize()
+
+    def all_reduce(y):
+        if world > 1:
+            dist.all_reduce(y)
+        return y
+
+    def lin_ops(x, l):                                               # model.py:158-160 on the drop-in operators
+        xq, xs = kernel.act_quant(x)
+        return kernel.fp8_gemm(xq, xs, l.weight, l.weight.scale)
+
+    def lin_seam(x, l):
+        return L.linear(x, l.weight)
+
+    def mlp(x, e, lin, reduce=True):
+        y = lin(F.silu(lin(x, e.w1)) * lin(x, e.w3), e.w2)
+        return all_reduce(y) if reduce else y
+
+    def moe_loop(m, x):                                              # MoE.forward, model.py:669-693
+        weights, indices = m.gate(x)
+        y = torch.zeros_like(x)
+        counts = torch.bincount(indices.flatten(), minlength=E).tolist()
+        for i in range(start, start + n_local):
+            if counts[i] == 0:
+                continue
+            idx, top = torch.where(indices == i)
+            y[idx] += mlp(x[idx], m.experts[i], lin_ops, reduce=False) * weights[idx, top, None]
+        z = mlp(x, m.shared, lin_ops)
+        return all_reduce(y) + z
+
+    def moe_grouped(m, x):
+        m.shared_experts = lambda t: mlp(t, m.shared, lin_seam)
+        return dsv3_b200.grouped_moe_forward(m, x, world_size=world)
+
+    def step(x, a_in, seams):
+        lin = lin_seam if seams else lin_ops
+        out = None
+        for layer in range(n_layers):
+            if seams:
+                L.reset_memo()      # every layer has its own input in the model: no reuse of a quantisation across layers
+            a = attn[layer % len(attn)]
+            q = lin(lin(x, a.wq_a), a.wq_b)                           # model.py:464 (q_norm is outside the path)
+            kv = lin(x, a.wkv_a)                                      # model.py:468
+            wkv_b = kernel.weight_dequant(a.wkv_b.weight, a.wkv_b.weight.scale)     # model.py:481
+            o = all_reduce(lin(a_in, a.wo))                           # model.py:496, 263-264
+            if layer < n_dense:
+                out = mlp(x, dense[layer % len(dense)], lin)
+            else:
+                m = moes[layer % len(moes)]
+                out = moe_grouped(m, x) if seams else moe_loop(m, x)
+        return out, q, kv, wkv_b, o
+
+    side = torch.cuda.Stream(device=dev)
+    results = {}
+    for B in [int(v) for v in args.decode_batch.split(",")]:
+        xg = torch.Generator(device=dev).manual_seed(9)               # the same tokens on every rank
+        x = torch.randn(B, dim, device=dev, dtype=torch.float32, generator=xg).to(torch.bfloat16)
+        a_in = torch.randn(B, heads * vdim // world, device=dev, dtype=torch.float32, generator=xg).to(torch.bfloat16)
+        # weight bytes a step touches on this rank: everything but the routed experts no token of the batch chose
+        with torch.no_grad():
+            touched = 0
+            for layer in range(n_dense, n_layers):
+                _, idx = moes[layer % len(moes)].gate(x)
+                loc = idx[(idx >= start) & (idx < start + n_local)]
+                touched += int(torch.unique(loc).numel()) * 3 * dim * moe_inter
+        step_bytes = (n_layers * attn[0].bytes + n_dense * dense[0].bytes + (n_layers - n_dense) * 3 * dim * (moe_inter // world) + touched)
+        res = {}
+
+        def timed(fn, reps):
+            fn()
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            t = e0.elapsed_time(e1) / reps
+            if world > 1:
+                tt = torch.tensor([t], device=dev, dtype=torch.float64)
+                dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+                t = tt.item()
+            return t
+
+        with torch.cuda.stream(side), torch.no_grad():
+            dsv3_b200.disable_weight_dequant_cache()
+            if not args.decode_skip_operators:
+                res["operators_ms"] = timed(lambda: step(x, a_in, False), 1)
+            dsv3_b200.enable_weight_dequant_cache(4 << 30)
+            L.reset_memo()
+            res["seams_ms"] = timed(lambda: step(x, a_in, True), max(2, args.steps))
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                outs = step(x, a_in, True)
+            res["graph_ms"] = timed(g.replay, max(3, args.steps))
+            del g, outs
+        dsv3_b200.check_device_status()
+        best = res["graph_ms"]
+        res.update(batch=B, tokens_per_s=B / (best * 1e-3), step_weight_bytes=step_bytes,
+                   hbm_gbs=step_bytes / (best * 1e-3) / 1e9, frac_of_hbm=step_bytes / (best * 1e-3) / 1e9 / peaks["hbm_gbs"])
+        results[f"B={B}"] = res
+    dsv3_b200.disable_weight_dequant_cache()
+    if rank == 0:
+        sys.stdout.flush()
+        os.dup2(saved_stdout, 1)
+        first = results[next(iter(results))]
+        print(json.dumps({
+            "metric": "decode_tokens_per_s_671B_shapes_gemm_path", "value": first["tokens_per_s"], "unit": "tokens/s",
+            "n_gpus": world, "steps": max(3, args.steps), "warmup": 1, "ms_per_step": first["graph_ms"], "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 x fp8_e4m3 -> fp32", "data": "synthetic",
+            "config": {"workload": f"BASELINE configs[4] on the GEMM path: 61 layers of DeepSeek-V3 671B Linear shapes at TP={world}, "
+                                   f"one decode step (M = batch rows), {n_inst} distinct instances per layer kind visited in rotation; "
+                                   "attention scores, RoPE, norms, embedding and head are not executed",
+                       "batches": args.decode_batch},
+            "per_batch": results,
+        }), flush=True)
+        os.dup2(2, 1)
+    if world > 1:
+        killer = threading.Timer(45.0, lambda: os._exit(0))
+        killer.daemon = True
+        killer.start()
+        torch.cuda.synchronize()
+        dist.barrier()
+        dist.destroy_process_group()
+        killer.cancel()
+
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -944,8 +1165,14 @@ def main():
     ap.add_argument("--moe-layer", action="store_true", help="BASELINE configs[2]: one MoE layer, expert loop vs grouped")
     ap.add_argument("--moe-tokens", type=int, default=2048)
     ap.add_argument("--moe-experts", type=int, default=256)
+    ap.add_argument("--decode-step", action="store_true", help="BASELINE configs[4] on the GEMM path: one 671B-shaped decode step")
+    ap.add_argument("--decode-batch", default="1,16,64")
+    ap.add_argument("--decode-instances", type=int, default=2, help="distinct weight instances per layer kind")
+    ap.add_argument("--decode-skip-operators", action="store_true", help="skip the slow reference-structure mode")
     args = ap.parse_args()
-    if args.moe_layer:
+    if args.decode_step:
+        run_decode_step(args)
+    elif args.moe_layer:
         run_moe_layer(args)
     elif args.single:
         run_single(args)

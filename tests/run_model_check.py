@@ -3,8 +3,10 @@
 same GPU and the same random weights, on top of the reference's own ``kernel.py``; compares logits
 and greedy tokens.
 
-    python deepseek-v3_b200/run_model_check.py --reference-dir <DeepSeek-V3>/inference \
-        [--config configs/config_16B.json] [--n-layers 4] [--batch 4] [--prompt-len 128] [--new-tokens 32]
+    python tests/run_model_check.py --reference-dir <DeepSeek-V3>/inference \
+        [--config configs/config_16B.json] [--n-layers 27] [--batch 32] [--prompt-len 1024] [--new-tokens 32] [--seams] [--graph]
+
+A tool, not a pytest module: it needs the reference's source tree, which the committed tests must not depend on.
 
 What it checks (the end-to-end parity targets): relative RMS difference of the logits of the prefill
 and of every decode step (target <= 2e-2), and the fraction of decode steps whose greedy token is the
@@ -13,6 +15,16 @@ does not cascade.  Because the reference's own result depends on which of its ti
 autotuner picked, the same comparison is also made between two of the reference's configurations
 (16x32 and 64x128 tiles): that is the reference's numerical noise on the model at hand, and on a
 random-initialised model (near-uniform logits) it can exceed the targets by itself.
+
+To make the token criterion decidable on such a model, the match is also reported over the DECIDABLE steps only:
+those where the reference's margin between its best and second-best logit exceeds four times the RMS difference
+between the reference's own two tile configurations at that step.  Where the margin is smaller, the reference's
+greedy token is decided by its own rounding noise and no implementation, the reference included, can be expected to
+reproduce it.  `pass_decidable` is: token match >= 99 % over the decidable steps, and logits within 2e-2 relative
+RMS or within 1.25 x the reference's own noise, whichever is larger.
+
+--graph additionally captures one decode step (seqlen 1 at a fixed position, seams installed: no host
+synchronisation is left in the forward) in a CUDA graph and reports eager against replayed time per step.
 
 Notes taken from the reference: ``model.gemm_impl`` must be set to "fp8" or ``linear()`` never reaches
 ``act_quant``/``fp8_gemm`` (model.py:16,155); weights are written in place because replacing a
@@ -30,7 +42,7 @@ import os
 import sys
 import time
 
-HERE = os.path.dirname(os.path.abspath(__file__))
+HERE = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "deepseek-v3_b200")
 
 
 def main() -> None:
@@ -44,6 +56,8 @@ def main() -> None:
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--seams", action="store_true",
                     help="also run with dsv3_b200.install_linear / install_moe (shared quantisation, grouped MoE)")
+    ap.add_argument("--graph", action="store_true", help="with --seams: time one decode step eagerly and as a replayed CUDA graph")
+    ap.add_argument("--skip-noise", action="store_true", help="skip the two fixed-tile runs of the reference")
     ap.add_argument("--out", default=None, help="write the result as JSON to this file")
     args = ap.parse_args()
 
@@ -147,22 +161,57 @@ def main() -> None:
     run(ours, forced=tok_ref)
     lg_ours, tok_ours, dt_ours = run(ours, forced=tok_ref)
     dsv3_b200.check_device_status()
-    small, large = FixedTile(16, 32), FixedTile(64, 128)
-    run(small, forced=tok_ref)
-    lg_small, tok_small, _ = run(small, forced=tok_ref)
-    run(large, forced=tok_ref)
-    lg_large, tok_large, _ = run(large, forced=tok_ref)
+    if args.skip_noise:
+        lg_small = lg_large = lg_ref
+        tok_small = tok_large = tok_ref
+    else:
+        small, large = FixedTile(16, 32), FixedTile(64, 128)
+        run(small, forced=tok_ref)
+        lg_small, tok_small, _ = run(small, forced=tok_ref)
+        run(large, forced=tok_ref)
+        lg_large, tok_large, _ = run(large, forced=tok_ref)
     use(ours)
     seam = None
+    graph_res = None
     if args.seams:
         orig_linear, orig_moe = M.linear, M.MoE.forward
-        dsv3_b200.install_linear(M)
+        dsv3_b200.install_linear(M, assume_no_inplace=True)      # model.py never modifies a projection's input in place
         dsv3_b200.install_moe(M)
+        dsv3_b200.enable_weight_dequant_cache(2 << 30)           # wkv_b of every layer (model.py:481)
         run(ours, forced=tok_ref)
         lg_seam, tok_seam, dt_seam = run(ours, forced=tok_ref)
         dsv3_b200.check_device_status()
-        M.linear, M.MoE.forward = orig_linear, orig_moe
         seam = (lg_seam, tok_seam, dt_seam)
+        if args.graph:
+            # one decode step at a fixed position: with both seams installed the forward has no host synchronisation
+            pos = args.prompt_len + args.new_tokens - 2
+            nxt = tok_ref[-2].view(-1, 1).clone()
+            side = torch.cuda.Stream()
+            with torch.cuda.stream(side), torch.inference_mode():
+                for _ in range(2):
+                    eager_out = model.forward(nxt, pos)
+                side.synchronize()
+                t0 = time.perf_counter()
+                for _ in range(10):
+                    eager_out = model.forward(nxt, pos)
+                side.synchronize()
+                eager_ms = (time.perf_counter() - t0) / 10 * 1e3
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    graph_out = model.forward(nxt, pos)
+                g.replay()
+                side.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(10):
+                    g.replay()
+                e1.record()
+                side.synchronize()
+                graph_res = {"position": pos, "eager_ms_per_step": eager_ms, "replayed_ms_per_step": e0.elapsed_time(e1) / 10,
+                             "same_logits_as_eager": bool(torch.equal(graph_out, eager_out))}
+            dsv3_b200.check_device_status()
+        dsv3_b200.disable_weight_dequant_cache()
+        M.linear, M.MoE.forward = orig_linear, orig_moe
 
     def rel_rms(a, b):
         return ((a - b).pow(2).mean().sqrt() / b.pow(2).mean().sqrt()).item()
@@ -171,6 +220,14 @@ def main() -> None:
     match = (tok_ours == tok_ref).float().mean().item()
     noise = [rel_rms(lg_small[i], lg_large[i]) for i in range(lg_ref.size(0))]
     noise_match = (tok_small == tok_large).float().mean().item()
+    # decidable steps: reference margin (best minus second-best logit) against the reference's own tile-config noise
+    top2 = lg_ref.topk(2, dim=-1).values                                     # [steps, batch, 2]
+    margin = top2[..., 0] - top2[..., 1]
+    sigma = (lg_small - lg_large).pow(2).mean(dim=-1).sqrt()                 # [steps, batch]
+    decidable = margin > 4.0 * sigma
+    n_dec = int(decidable.sum())
+    match_dec = ((tok_ours == tok_ref) & decidable).sum().item() / max(1, n_dec)
+    noise_match_dec = ((tok_small == tok_large) & decidable).sum().item() / max(1, n_dec)
     vs_small = max(rel_rms(lg_ours[i], lg_small[i]) for i in range(lg_ref.size(0)))
     vs_large = max(rel_rms(lg_ours[i], lg_large[i]) for i in range(lg_ref.size(0)))
     res = {
@@ -186,7 +243,11 @@ def main() -> None:
             "logits_rel_rms_max_vs_this_library_without_seams": max(rel_rms(seam[0][i], lg_ours[i]) for i in range(lg_ref.size(0))),
             "greedy_token_match_vs_reference": (seam[1] == tok_ref).float().mean().item(),
             "decode_ms_per_step": seam[2] * 1e3},
+        "decidable_steps": n_dec, "greedy_token_match_decidable": match_dec,
+        "reference_noise_greedy_token_match_decidable": noise_match_dec,
+        "graph": graph_res,
         "pass": bool(max(per_step) <= 2e-2 and match >= 0.99),
+        "pass_decidable": bool(n_dec > 0 and match_dec >= 0.99 and max(per_step) <= max(2e-2, 1.25 * max(noise))),
         "within_reference_noise": bool(max(per_step) <= 1.5 * max(noise) and match >= noise_match - 0.05),
     }
     print(json.dumps(res), flush=True)
