@@ -941,7 +941,8 @@ def run_decode_step(args):
     keeps weights out of L2 between two uses without holding 85 GB per rank.
     Modes: `operators` = the reference's call structure on the drop-in operators (act_quant + fp8_gemm per Linear,
     Python expert loop with its host synchronisations); `seams` = linear seam (fused decode Linear), grouped MoE,
-    weight_dequant cache; `graph` = the seams step captured once in a CUDA graph and replayed."""
+    weight_dequant cache, SwiGLU folded into the quantisation; `graph` = the seams step captured once in a CUDA graph and
+    replayed."""
     import torch
     import torch.distributed as dist
     import torch.nn.functional as F
@@ -964,7 +965,9 @@ def run_decode_step(args):
     dim, q_lora, kv_lora, rope, heads, nope, vdim = 7168, 1536, 512, 64, 128, 128, 128
     inter, moe_inter, E, topk, n_groups, topk_groups, route_scale = 18432, 2048, 256, 8, 8, 4, 2.5
     n_layers, n_dense = 61, 3
-    n_local = E // world
+    # shard shapes: the real world size, or (single process) the per-rank shapes of a larger tensor-parallel group
+    tp = args.decode_tp_shapes if (world == 1 and args.decode_tp_shapes > 0) else world
+    n_local = E // tp
     start = rank * n_local
     gen = torch.Generator(device=dev).manual_seed(4000 + rank)
 
@@ -983,14 +986,14 @@ def run_decode_step(args):
 
     class Attn:
         def __init__(self):
-            self.wq_a, self.wq_b = Lin(q_lora, dim), Lin(heads * (nope + rope) // world, q_lora)
-            self.wkv_a, self.wkv_b = Lin(kv_lora + rope, dim), Lin(heads * (nope + vdim) // world, kv_lora)
-            self.wo = Lin(dim, heads * vdim // world)
+            self.wq_a, self.wq_b = Lin(q_lora, dim), Lin(heads * (nope + rope) // tp, q_lora)
+            self.wkv_a, self.wkv_b = Lin(kv_lora + rope, dim), Lin(heads * (nope + vdim) // tp, kv_lora)
+            self.wo = Lin(dim, heads * vdim // tp)
             self.bytes = sum(l.bytes for l in (self.wq_a, self.wq_b, self.wkv_a, self.wkv_b, self.wo))
 
     class Dense:
         def __init__(self):
-            self.w1, self.w3, self.w2 = Lin(inter // world, dim), Lin(inter // world, dim), Lin(dim, inter // world)
+            self.w1, self.w3, self.w2 = Lin(inter // tp, dim), Lin(inter // tp, dim), Lin(dim, inter // tp)
             self.bytes = 3 * self.w1.bytes
 
     class MoE:
@@ -998,7 +1001,7 @@ def run_decode_step(args):
             self.dim, self.n_routed_experts, self.n_local_experts, self.n_activated_experts = dim, E, n_local, topk
             self.experts_start_idx, self.experts_end_idx = start, start + n_local
             self.experts = [Expert(dim, moe_inter) if start <= i < start + n_local else None for i in range(E)]
-            self.shared = Expert(dim, moe_inter // world)
+            self.shared = Expert(dim, moe_inter // tp)
             g2 = torch.Generator(device=dev).manual_seed(77)          # the gate is replicated: same on every rank
             self.gate_w = (torch.randn(E, dim, device=dev, dtype=torch.float32, generator=g2) * 0.02).to(torch.bfloat16)
             self.gate_b = torch.randn(E, device=dev, dtype=torch.float32, generator=g2) * 0.01
@@ -1027,15 +1030,29 @@ def run_decode_step(args):
             dist.all_reduce(y)
         return y
 
+    ops = {"k": kernel}       # the operator module the `operators` mode calls (the drop-in, or the reference's own)
+
     def lin_ops(x, l):                                               # model.py:158-160 on the drop-in operators
-        xq, xs = kernel.act_quant(x)
-        return kernel.fp8_gemm(xq, xs, l.weight, l.weight.scale)
+        xq, xs = ops["k"].act_quant(x)
+        return ops["k"].fp8_gemm(xq, xs, l.weight, l.weight.scale)
+
+    ref_kernel = None
+    if args.reference_kernel_dir:
+        # builder-run comparison only: the reference's own kernel.py (Triton), imported from a directory outside the repo
+        import importlib.util
+        spec = importlib.util.spec_from_file_location("_reference_kernel", os.path.join(args.reference_kernel_dir, "kernel.py"))
+        ref_kernel = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(ref_kernel)
 
     def lin_seam(x, l):
         return L.linear(x, l.weight)
 
     def mlp(x, e, lin, reduce=True):
-        y = lin(F.silu(lin(x, e.w1)) * lin(x, e.w3), e.w2)
+        if lin is lin_seam:                                          # the MLP seam: SwiGLU folded into the quantisation
+            hq, hs = dsv3_b200.swiglu_quant(lin(x, e.w1), lin(x, e.w3))
+            y = kernel.fp8_gemm(hq, hs, e.w2.weight, e.w2.weight.scale)
+        else:
+            y = lin(F.silu(lin(x, e.w1)) * lin(x, e.w3), e.w2)      # model.py:532, 633
         return all_reduce(y) if reduce else y
 
     def moe_loop(m, x):                                              # MoE.forward, model.py:669-693
@@ -1063,7 +1080,7 @@ def run_decode_step(args):
             a = attn[layer % len(attn)]
             q = lin(lin(x, a.wq_a), a.wq_b)                           # model.py:464 (q_norm is outside the path)
             kv = lin(x, a.wkv_a)                                      # model.py:468
-            wkv_b = kernel.weight_dequant(a.wkv_b.weight, a.wkv_b.weight.scale)     # model.py:481
+            wkv_b = (kernel if seams else ops["k"]).weight_dequant(a.wkv_b.weight, a.wkv_b.weight.scale)     # model.py:481
             o = all_reduce(lin(a_in, a.wo))                           # model.py:496, 263-264
             if layer < n_dense:
                 out = mlp(x, dense[layer % len(dense)], lin)
@@ -1077,7 +1094,7 @@ def run_decode_step(args):
     for B in [int(v) for v in args.decode_batch.split(",")]:
         xg = torch.Generator(device=dev).manual_seed(9)               # the same tokens on every rank
         x = torch.randn(B, dim, device=dev, dtype=torch.float32, generator=xg).to(torch.bfloat16)
-        a_in = torch.randn(B, heads * vdim // world, device=dev, dtype=torch.float32, generator=xg).to(torch.bfloat16)
+        a_in = torch.randn(B, heads * vdim // tp, device=dev, dtype=torch.float32, generator=xg).to(torch.bfloat16)
         # weight bytes a step touches on this rank: everything but the routed experts no token of the batch chose
         with torch.no_grad():
             touched = 0
@@ -1085,7 +1102,7 @@ def run_decode_step(args):
                 _, idx = moes[layer % len(moes)].gate(x)
                 loc = idx[(idx >= start) & (idx < start + n_local)]
                 touched += int(torch.unique(loc).numel()) * 3 * dim * moe_inter
-        step_bytes = (n_layers * attn[0].bytes + n_dense * dense[0].bytes + (n_layers - n_dense) * 3 * dim * (moe_inter // world) + touched)
+        step_bytes = (n_layers * attn[0].bytes + n_dense * dense[0].bytes + (n_layers - n_dense) * 3 * dim * (moe_inter // tp) + touched)
         res = {}
 
         def timed(fn, reps):
@@ -1108,6 +1125,11 @@ def run_decode_step(args):
 
         with torch.cuda.stream(side), torch.no_grad():
             dsv3_b200.disable_weight_dequant_cache()
+            if ref_kernel is not None:
+                ops["k"] = ref_kernel
+                step(x, a_in, False)                                  # Triton JIT + autotune
+                res["reference_kernels_ms"] = timed(lambda: step(x, a_in, False), 1)
+                ops["k"] = kernel
             if not args.decode_skip_operators:
                 res["operators_ms"] = timed(lambda: step(x, a_in, False), 1)
             dsv3_b200.enable_weight_dequant_cache(4 << 30)
@@ -1132,7 +1154,8 @@ def run_decode_step(args):
             "metric": "decode_tokens_per_s_671B_shapes_gemm_path", "value": first["tokens_per_s"], "unit": "tokens/s",
             "n_gpus": world, "steps": max(3, args.steps), "warmup": 1, "ms_per_step": first["graph_ms"], "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 x fp8_e4m3 -> fp32", "data": "synthetic",
-            "config": {"workload": f"BASELINE configs[4] on the GEMM path: 61 layers of DeepSeek-V3 671B Linear shapes at TP={world}, "
+            "config": {"workload": f"BASELINE configs[4] on the GEMM path: 61 layers of DeepSeek-V3 671B Linear shapes at TP={tp}"
+                                   + (" (one rank's shards on one GPU, no collectives)" if tp != world else "") + ", "
                                    f"one decode step (M = batch rows), {n_inst} distinct instances per layer kind visited in rotation; "
                                    "attention scores, RoPE, norms, embedding and head are not executed",
                        "batches": args.decode_batch},
@@ -1168,7 +1191,12 @@ def main():
     ap.add_argument("--decode-step", action="store_true", help="BASELINE configs[4] on the GEMM path: one 671B-shaped decode step")
     ap.add_argument("--decode-batch", default="1,16,64")
     ap.add_argument("--decode-instances", type=int, default=2, help="distinct weight instances per layer kind")
+    ap.add_argument("--decode-tp-shapes", type=int, default=0,
+                    help="single process only: use one rank's shard shapes of a TP group of this size (no collectives)")
     ap.add_argument("--decode-skip-operators", action="store_true", help="skip the slow reference-structure mode")
+    ap.add_argument("--reference-kernel-dir", default=None,
+                    help="--decode-step only: directory holding the reference's kernel.py; adds the reference-structure mode on "
+                         "the reference's own Triton kernels (a comparison for whoever has the reference at hand; never needed)")
     args = ap.parse_args()
     if args.decode_step:
         run_decode_step(args)

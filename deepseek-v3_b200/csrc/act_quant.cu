@@ -88,6 +88,51 @@ __global__ void __launch_bounds__(kThreads) act_quant_generic_kernel(const uint4
     }
 }
 
+// SwiGLU followed by act_quant in one pass: h = bf16(bf16(silu(a)) * b), then h is quantised per 128 values.
+// Replaces the three launches `F.silu(w1(x)) * w3(x)` + act_quant in front of w2 (model.py:532, 633 and 158-159) and
+// keeps their rounding points: silu is evaluated in fp32 as a / (1 + exp(-a)) and rounded to bf16, the product is
+// formed in fp32 and rounded to bf16 (what the framework's bf16 kernels do), and the quantisation of h is the
+// arithmetic of act_quant128_kernel.  h itself is never written.
+__device__ __forceinline__ uint32_t swiglu2(uint32_t a2, uint32_t b2) {
+    const float al = bf16_bits_to_float(a2 & 0xFFFFu), ah = __uint_as_float(a2 & 0xFFFF0000u);
+    const float bl = bf16_bits_to_float(b2 & 0xFFFFu), bh = __uint_as_float(b2 & 0xFFFF0000u);
+    const float sl = __bfloat162float(__float2bfloat16_rn(al / (1.0f + expf(-al))));
+    const float sh = __bfloat162float(__float2bfloat16_rn(ah / (1.0f + expf(-ah))));
+    return pack_bf16x2(sl * bl, sh * bh);
+}
+
+__global__ void __launch_bounds__(kThreads, 4) swiglu_quant128_kernel(const uint4* __restrict__ a, const uint4* __restrict__ b,
+                                                                    uint2* __restrict__ y, float* __restrict__ s, int64_t nblk,
+                                                                    int scale_fmt) {
+    griddep_launch_dependents();
+    griddep_wait();
+    const int lane16 = threadIdx.x & 15;
+    const int64_t b0 = static_cast<int64_t>(blockIdx.x) * kBlocksPerCta + (threadIdx.x >> 4);
+    uint4 va[kUnroll], vb[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+        const int64_t blk = b0 + u * (kThreads / 16);
+        va[u] = (blk < nblk) ? __ldcs(a + blk * 16 + lane16) : make_uint4(0, 0, 0, 0);
+        vb[u] = (blk < nblk) ? __ldcs(b + blk * 16 + lane16) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+        const int64_t blk = b0 + u * (kThreads / 16);
+        const uint4 h = make_uint4(swiglu2(va[u].x, vb[u].x), swiglu2(va[u].y, vb[u].y), swiglu2(va[u].z, vb[u].z),
+                                   swiglu2(va[u].w, vb[u].w));
+        float m = amax8(h);
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 4));
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+        const float sc = scale_from_amax(m, scale_fmt);
+        if (blk < nblk) {
+            y[blk * 16 + lane16] = (scale_fmt == DSV3_SCALE_FMT_FP32) ? quant8<true>(h, sc) : quant8<false>(h, sc);
+            if (lane16 == 0) s[blk] = sc;
+        }
+    }
+}
+
 }  // namespace
 
 int launch_act_quant(const void* x, int64_t rows, int64_t K, int block_size, int scale_fmt, void* y, float* s,
@@ -112,6 +157,21 @@ int launch_act_quant(const void* x, int64_t rows, int64_t K, int block_size, int
                                        scale_fmt));
     }
     DSV3_CUDA_TRY(cudaGetLastError());
+    return DSV3_OK;
+}
+
+int launch_swiglu_quant(const void* a, const void* b, int64_t rows, int64_t K, int scale_fmt, void* y, float* s,
+                        cudaStream_t stream) {
+    const int64_t nblk = rows * (K / 128);
+    if (nblk == 0) return DSV3_OK;
+    const int64_t grid = (nblk + kBlocksPerCta - 1) / kBlocksPerCta;
+    if (grid >= (1ll << 31)) {
+        set_last_error("swiglu_quant: too many blocks (%lld)", static_cast<long long>(nblk));
+        return DSV3_ERR_UNSUPPORTED;
+    }
+    DSV3_CUDA_TRY(launch_dependent(swiglu_quant128_kernel, dim3(static_cast<unsigned>(grid)), dim3(kThreads), 0, stream,
+                                   static_cast<const uint4*>(a), static_cast<const uint4*>(b), static_cast<uint2*>(y), s, nblk,
+                                   scale_fmt));
     return DSV3_OK;
 }
 

@@ -13,6 +13,8 @@ namespace dsv3 {
 // kernels (one translation unit each)
 int launch_act_quant(const void* x, int64_t rows, int64_t K, int block_size, int scale_fmt, void* y, float* s,
                      cudaStream_t stream);
+int launch_swiglu_quant(const void* a, const void* b, int64_t rows, int64_t K, int scale_fmt, void* y, float* s,
+                        cudaStream_t stream);
 int launch_weight_dequant(const void* w, const float* s, int64_t N, int64_t K, int block, void* y, cudaStream_t stream);
 int launch_weight_quant(const void* w, int64_t N, int64_t K, void* q, float* s, cudaStream_t stream);
 int launch_fp8_gemm_simple(const void* a, const float* a_s, const void* b, const float* b_s, int64_t M, int64_t N,
@@ -129,6 +131,32 @@ int dsv3_act_quant(const void* x, int64_t rows, int64_t K, int block_size, int s
         return DSV3_ERR_UNSUPPORTED;
     }
     return launch_act_quant(x, rows, K, block_size, scale_fmt, y, s, static_cast<cudaStream_t>(stream));
+}
+
+int dsv3_swiglu_quant(const void* a, const void* b, int64_t rows, int64_t K, int scale_fmt, void* y, float* s,
+                      dsv3_stream_t stream) {
+    if (rows < 0 || K < 0) {
+        set_last_error("swiglu_quant: negative size");
+        return DSV3_ERR_INVALID_ARGUMENT;
+    }
+    if (K % 128 != 0) {
+        set_last_error("swiglu_quant: last dimension %lld is not divisible by 128", (long long)K);
+        return DSV3_ERR_INVALID_ARGUMENT;
+    }
+    if (scale_fmt != DSV3_SCALE_FMT_FP32 && scale_fmt != DSV3_SCALE_FMT_UE8M0) {
+        set_last_error("swiglu_quant: unknown scale_fmt %d", scale_fmt);
+        return DSV3_ERR_INVALID_ARGUMENT;
+    }
+    if (rows == 0 || K == 0) return DSV3_OK;
+    if (is_null(a) || is_null(b) || is_null(y) || is_null(s)) {
+        set_last_error("swiglu_quant: null pointer");
+        return DSV3_ERR_INVALID_ARGUMENT;
+    }
+    if (reinterpret_cast<uintptr_t>(a) % 16 != 0 || reinterpret_cast<uintptr_t>(b) % 16 != 0 || reinterpret_cast<uintptr_t>(y) % 8 != 0) {
+        set_last_error("swiglu_quant: a and b must be 16-byte and y 8-byte aligned");
+        return DSV3_ERR_UNSUPPORTED;
+    }
+    return launch_swiglu_quant(a, b, rows, K, scale_fmt, y, s, static_cast<cudaStream_t>(stream));
 }
 
 int dsv3_weight_dequant(const void* w, const float* s, int64_t N, int64_t K, int block_size, void* y,

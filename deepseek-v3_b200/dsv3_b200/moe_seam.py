@@ -16,12 +16,11 @@ import ctypes
 from typing import List
 
 import torch
-import torch.nn.functional as F
 
 from . import _lib
 from ._lib import lib
 from .linear_seam import _quantised
-from .ops import act_quant, _stream
+from .ops import swiglu_quant, _stream
 
 
 class GroupedExperts:
@@ -84,8 +83,7 @@ class GroupedExperts:
             xq_p = xq.view(torch.uint8).index_select(0, tok).view(torch.float8_e4m3fn)
             xs_p = xs.index_select(0, tok)
             # ---- w2(silu(w1 x) * w3 x), the bf16 rounding points of Expert.forward (model.py:633)
-            h = F.silu(self.gemm("w1", xq_p, xs_p, seg, hint)) * self.gemm("w3", xq_p, xs_p, seg, hint)
-            hq, hs = act_quant(h, 128, self.scale_fmt)
+            hq, hs = swiglu_quant(self.gemm("w1", xq_p, xs_p, seg, hint), self.gemm("w3", xq_p, xs_p, seg, hint), self.scale_fmt)
             o = self.gemm("w2", hq, hs, seg, hint)
             # ---- y[t] = sum over the token's local experts, ascending expert id, bf16 at every step
             y = torch.empty(T, self.dim, dtype=torch.bfloat16, device=x.device)

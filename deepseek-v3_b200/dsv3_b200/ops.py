@@ -82,6 +82,24 @@ def act_quant(x: torch.Tensor, block_size: int = 128, scale_fmt: Optional[str] =
     return y, s
 
 
+def swiglu_quant(a: torch.Tensor, b: torch.Tensor, scale_fmt: Optional[str] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``act_quant(F.silu(a) * b, 128, scale_fmt)`` in one launch (model.py:532 / 633 followed by :158-159), with the
+    rounding points of the three-launch form; the bf16 product is never written."""
+    assert a.is_contiguous() and b.is_contiguous(), 'Input tensors must be contiguous'
+    assert a.shape == b.shape and a.size(-1) % 128 == 0, 'a and b must have the same shape, last dimension divisible by 128'
+    dev = _require_cuda(a, b)
+    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
+        raise NotImplementedError("swiglu_quant takes bfloat16 tensors")
+    K = a.size(-1)
+    rows = a.numel() // K if K else 0
+    y = torch.empty_like(a, dtype=torch.float8_e4m3fn)
+    s = a.new_empty(*a.size()[:-1], K // 128, dtype=torch.float32)
+    with torch.cuda.device(dev):
+        _lib.check(lib.dsv3_swiglu_quant(a.data_ptr(), b.data_ptr(), rows, K, 1 if scale_fmt == "ue8m0" else 0,
+                                         y.data_ptr(), s.data_ptr(), _stream()))
+    return y, s
+
+
 # Cache of de-quantised weights (off by default).  MLA.forward in "absorb" mode de-quantises wkv_b on every call of
 # every layer (model.py:481) although the weight never changes; with the cache on, the call after the first returns
 # the tensor computed before and launches nothing.  An entry is keyed on the weight's and the scales' storage

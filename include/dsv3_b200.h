@@ -57,6 +57,17 @@ int dsv3_act_quant(const void* x, int64_t rows, int64_t K, int block_size, int s
                    void* y, float* s, dsv3_stream_t stream);
 
 /*
+ * SwiGLU + act_quant in one launch -- replaces `F.silu(w1(x)) * w3(x)` (model.py:532, 633) together with the
+ * act_quant that linear() applies to the product in front of w2 (model.py:158-159).
+ *   a, b : bf16 [rows, K] (the outputs of w1 and w3), K % 128 == 0
+ *   y    : e4m3 [rows, K]    s : fp32 [rows, K / 128]
+ * h = bf16(bf16(silu(a)) * b) with the rounding points of the framework's bf16 kernels, then (y, s) = act_quant(h);
+ * h is not written.  Bit-identical to the three-launch form.
+ */
+int dsv3_swiglu_quant(const void* a, const void* b, int64_t rows, int64_t K, int scale_fmt, void* y, float* s,
+                      dsv3_stream_t stream);
+
+/*
  * weight_dequant -- replaces kernel.py:89-110 (kernel :60-86).
  *   w : e4m3 [N, K]   s : fp32 [ceil(N/block), ceil(K/block)]   y : bf16 [N, K]
  *   y = bf16(float(w) * s[n / block, k / block])

@@ -174,9 +174,10 @@ def main() -> None:
     seam = None
     graph_res = None
     if args.seams:
-        orig_linear, orig_moe = M.linear, M.MoE.forward
+        orig_linear, orig_moe, orig_mlp, orig_expert = M.linear, M.MoE.forward, M.MLP.forward, M.Expert.forward
         dsv3_b200.install_linear(M, assume_no_inplace=True)      # model.py never modifies a projection's input in place
         dsv3_b200.install_moe(M)
+        dsv3_b200.install_mlp(M)
         dsv3_b200.enable_weight_dequant_cache(2 << 30)           # wkv_b of every layer (model.py:481)
         run(ours, forced=tok_ref)
         lg_seam, tok_seam, dt_seam = run(ours, forced=tok_ref)
@@ -211,7 +212,7 @@ def main() -> None:
                              "same_logits_as_eager": bool(torch.equal(graph_out, eager_out))}
             dsv3_b200.check_device_status()
         dsv3_b200.disable_weight_dequant_cache()
-        M.linear, M.MoE.forward = orig_linear, orig_moe
+        M.linear, M.MoE.forward, M.MLP.forward, M.Expert.forward = orig_linear, orig_moe, orig_mlp, orig_expert
 
     def rel_rms(a, b):
         return ((a - b).pow(2).mean().sqrt() / b.pow(2).mean().sqrt()).item()

@@ -84,3 +84,54 @@ def test_linear_seam_matches_unfused_path_and_reuses_quantisation():
         dsv3_b200.check_device_status()
     finally:
         torch.set_default_dtype(torch.float32)
+
+
+def test_mlp_seam_matches_the_unfused_forward_bit_for_bit():
+    """install_mlp: MLP.forward / Expert.forward with SwiGLU folded into the quantisation, against
+    w2(F.silu(w1(x)) * w3(x)) on the same operators (model.py:532, 633)."""
+    import dsv3_b200
+    import kernel
+    import torch.nn.functional as F
+    torch.set_default_dtype(torch.bfloat16)
+    try:
+        class Lin:                                     # model.py's Linear: weight with a .scale attribute, bias, scale_fmt
+            def __init__(self, N, K, seed, bias=None):
+                _, self.weight = _weight(N, K, seed)
+                self.bias, self.scale_fmt = bias, None
+
+            def __call__(self, x):
+                xq, xs = kernel.act_quant(x, 128, self.scale_fmt)
+                y = kernel.fp8_gemm(xq, xs, self.weight, self.weight.scale)
+                return y if self.bias is None else y + self.bias
+
+        class RowParallelLinear(Lin):
+            pass
+
+        class MLP:
+            def __init__(self, dim, inter, row):
+                self.w1, self.w3 = Lin(inter, dim, 81), Lin(inter, dim, 82)
+                self.w2 = (RowParallelLinear if row else Lin)(dim, inter, 83, bias=torch.randn(dim, device="cuda").bfloat16())
+
+            def forward(self, x):
+                return self.w2(F.silu(self.w1(x)) * self.w3(x))
+
+        class Expert(MLP):
+            pass
+
+        calls = []
+        fake_dist = types.SimpleNamespace(all_reduce=lambda y: calls.append(tuple(y.shape)))
+        mod = types.SimpleNamespace(MLP=MLP, Expert=Expert, gemm_impl="fp8", block_size=128, world_size=2, dist=fake_dist)
+        x = O.randn_bf16((24, 512), 84, 1.0).cuda()
+        dsv3_b200.install_mlp(mod)
+        for cls, row in ((MLP, True), (Expert, False)):
+            m = cls(512, 384, row)
+            want = m.w2(F.silu(m.w1(x)) * m.w3(x))      # the reference's forward, spelled out
+            got = m.forward(x)
+            assert np.array_equal(bf16_bits(got), bf16_bits(want))
+            mod.gemm_impl = "bf16"                      # other modes fall back to the original forward
+            assert np.array_equal(bf16_bits(m.forward(x)), bf16_bits(want))
+            mod.gemm_impl = "fp8"
+        assert calls == [(24, 512)], "the all_reduce of a RowParallelLinear must follow its GEMM (model.py:263-264)"
+        dsv3_b200.check_device_status()
+    finally:
+        torch.set_default_dtype(torch.float32)

@@ -190,3 +190,22 @@ def test_weight_dequant_cache_skips_the_launch_for_an_unchanged_weight():
     finally:
         dsv3_b200.disable_weight_dequant_cache()
         torch.set_default_dtype(torch.float32)
+
+
+@pytest.mark.parametrize("rows,K,fmt", [(1, 128, None), (37, 2048, None), (300, 1408, None), (64, 2304, "ue8m0")])
+def test_swiglu_quant_equals_the_three_launch_form_bit_for_bit(rows, K, fmt):
+    """`dsv3_swiglu_quant` against `act_quant(F.silu(a) * b)` (model.py:532/633 followed by :158-159): same FP8 codes,
+    same scales.  Inputs include magnitudes where exp(-a) overflows or underflows and exact zeros."""
+    import dsv3_b200
+    import kernel
+    import torch.nn.functional as F
+    a = O.randn_bf16((rows, K), 700 + rows, 3.0)
+    b = O.randn_bf16((rows, K), 701 + rows, 1.0)
+    a[0, :8] = torch.tensor([-200.0, 200.0, 0.0, -0.0, 88.0, -88.0, 1e-3, -1e-3]).bfloat16()
+    b[0, 8:16] = 0.0
+    a, b = a.cuda(), b.cuda()
+    y, s = dsv3_b200.swiglu_quant(a, b, fmt)
+    y_ref, s_ref = kernel.act_quant(F.silu(a) * b, 128, fmt)
+    assert np.array_equal(u8(y), u8(y_ref))
+    assert np.array_equal(f32_bits(s), f32_bits(s_ref))
+    dsv3_b200.check_device_status()
