@@ -583,8 +583,9 @@ def run_ours(args):
     ratio_small = NCU_TRAFFIC["weight_major"][0] / gemm_bytes(*NCU_TRAFFIC["weight_major"][1])
     ach_big = big_f / big_t / 1e12 if big_t else None
     roofline = {
-        "kernel": "token-major tcgen05 kernels (launches with M >= 256): fp8_gemm_tm_kernel (CTA pairs, 256x128 tiles, K >= 1536) "
-                  "and fp8_gemm_tc_kernel<128,false> (short K, split-K)",
+        "kernel": "token-major tcgen05 kernels (launches with M >= 256): fp8_gemm_tw_kernel (CTA pairs, 256x256 tiles), "
+                  "fp8_gemm_tm_kernel (CTA pairs, 256x128 tiles, where 256-wide tiles fill the last round badly) "
+                  "and fp8_gemm_tc_kernel<128,false> (split-K)",
         "bound": "tensor", "achieved": ach_big, "peak": fp8_peak, "unit": "TFLOP/s",
         "frac": ach_big / fp8_peak if big_t else None,
         "frac_of_sustained": ach_big / fp8_sustained if big_t else None,

@@ -187,8 +187,8 @@ int dsv3_weight_quant(const void* w, int64_t N, int64_t K, void* q, float* s, ds
 }
 
 int dsv3_set_gemm_policy(int kernel, int split_k) {
-    if (kernel < 0 || kernel > 5 || split_k < 0 || split_k > 64) {
-        set_last_error("set_gemm_policy: kernel must be 0..5 and split_k 0..64");
+    if (kernel < 0 || kernel > 6 || split_k < 0 || split_k > 64) {
+        set_last_error("set_gemm_policy: kernel must be 0..6 and split_k 0..64");
         return DSV3_ERR_INVALID_ARGUMENT;
     }
     g_force_kernel = kernel;
@@ -268,6 +268,14 @@ int dsv3_fp8_linear(const void* x, int64_t M, int64_t K, const void* w, const fl
     return launch_fp8_linear_small(x, nullptr, nullptr, w, w_s, M, N, K, scale_fmt, c, static_cast<cudaStream_t>(stream));
 }
 
+int dsv3_selftest_bounded_wait(uint64_t limit_ns, dsv3_stream_t stream) {
+    if (limit_ns == 0 || limit_ns > 1000ull * 1000ull * 1000ull) {
+        set_last_error("selftest_bounded_wait: the limit must be between 1 ns and 1 s");
+        return DSV3_ERR_INVALID_ARGUMENT;
+    }
+    return launch_bounded_wait_selftest(limit_ns, static_cast<cudaStream_t>(stream));
+}
+
 int dsv3_check_device_status(dsv3_stream_t stream, uint32_t detail[4]) {
     DSV3_CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
     unsigned int* dptr = status_device_ptr();
@@ -278,8 +286,8 @@ int dsv3_check_device_status(dsv3_stream_t stream, uint32_t detail[4]) {
     if (host[0] == 0) return DSV3_OK;
     const unsigned int zero[4] = {0, 0, 0, 0};
     DSV3_CUDA_TRY(cudaMemcpy(dptr, zero, sizeof(zero), cudaMemcpyHostToDevice));
-    set_last_error("device wait gave up: kind=%u (1 smem-empty, 2 smem-full, 3 tmem-empty, 4 tmem-full, 5/6 group exchange, "
-                   "7/8 scale table) counter=%u cta=%u",
+    set_last_error("device wait gave up: kind=%u (1 smem-empty, 2 smem-full, 3 tmem-empty, 4 tmem-full, 7/8 scale table, "
+                   "9 self-test, 10 all-reduce peer signal) counter=%u cta=%u",
                    host[1], host[2], host[3]);
     return DSV3_ERR_DEVICE_TIMEOUT;
 }

@@ -837,6 +837,7 @@ TcPlan tc_plan(int64_t M, int64_t N, int64_t K, int force_kernel, int force_spli
     TcPlan pl;
     pl.error = DSV3_OK;
     pl.pair = false;
+    pl.wide = false;
     pl.splits = 1;
     pl.kc = static_cast<int>((K + kChunk - 1) / kChunk);
     pl.swap = (force_kernel == 3) || (force_kernel == 0 && M <= 64);
@@ -863,14 +864,14 @@ TcPlan tc_plan(int64_t M, int64_t N, int64_t K, int force_kernel, int force_spli
         if (splits > pl.kc) why = "more splits than 128-wide K chunks";
         else if (splits > 1 && tiles > kMaxTickets) why = "more output tiles than the workspace header has tickets";
         else if ((pl.kc + splits - 1) / splits > tab) why = "K range per split exceeds the weight-major kernel's scale table";
-        else if (force_kernel == 4 && splits > 1) why = "the CTA-pair kernel does not split K";
+        else if ((force_kernel == 4 || force_kernel == 6) && splits > 1) why = "the CTA-pair kernels do not split K";
         if (why) {
             set_last_error("fp8_gemm: pinned split factor %d cannot be used for M=%lld N=%lld K=%lld: %s", force_split,
                            static_cast<long long>(M), static_cast<long long>(N), static_cast<long long>(K), why);
             pl.error = DSV3_ERR_UNSUPPORTED;
             return pl;
         }
-    } else if (force_kernel == 4) {
+    } else if (force_kernel == 4 || force_kernel == 6) {
         splits = 1;
     } else if (tiles <= kMaxTickets) {
         // Splitting K fills idle SMs, but every split item pays for parking its partial tile, a fence and a
@@ -915,7 +916,31 @@ TcPlan tc_plan(int64_t M, int64_t N, int64_t K, int force_kernel, int force_spli
         pl.error = DSV3_ERR_UNSUPPORTED;
         return pl;
     }
-    pl.pair = !pl.swap && splits == 1 && (force_kernel == 4 || (force_kernel == 0 && tm_pair_supported(M, N, K, false)));
+    if (force_kernel == 6 && !tw_pair_supported(M, N, K, true)) {
+        set_last_error("fp8_gemm: the 256-wide CTA-pair kernel needs more than 128 tokens and more than 128 weight rows (M=%lld, N=%lld)",
+                       static_cast<long long>(M), static_cast<long long>(N));
+        pl.error = DSV3_ERR_UNSUPPORTED;
+        return pl;
+    }
+    if (!pl.swap && splits == 1) {
+        pl.pair = force_kernel == 4 || (force_kernel == 0 && tm_pair_supported(M, N, K, false));
+        pl.wide = force_kernel == 6;
+        if (force_kernel == 0 && tw_pair_supported(M, N, K, false)) {
+            // 256-wide pair tiles against the best 128-wide alternative, in units of one SM working through one
+            // 128 x 128 tile: rounds over the machine times the tile's size, times the measured cost per flop of
+            // the wide kernel relative to the alternative (B200: 0.90-0.94 for K >= 1536 against the 128-wide
+            // pair kernel, 0.79-0.80 for shorter K against the single-CTA kernel).  Wide tiles lose where they
+            // fill the machine's last round badly (few token tiles, N a small multiple of 256).
+            const int sms = num_sms(), pairs = sms / 2;
+            const int64_t pp = (static_cast<int64_t>(pl.tiles_p) + 1) / 2;
+            const int64_t t_wide = pp * ((N + 255) / 256);
+            const double cost_wide = static_cast<double>((t_wide + pairs - 1) / pairs) * 2.0 * (pl.kc >= 12 ? 0.92 : 0.80);
+            const double cost_narrow = pl.pair ? static_cast<double>((pp * pl.tiles_q + pairs - 1) / pairs)
+                                               : static_cast<double>((tiles + sms - 1) / sms);
+            pl.wide = cost_wide <= cost_narrow;
+        }
+        pl.pair = pl.pair || pl.wide;
+    }
     return pl;
 }
 
@@ -940,6 +965,7 @@ int launch_fp8_gemm_tc(const void* a, const float* a_s, const void* b, const flo
         }
     }
     if (pl.error != DSV3_OK) return pl.error;
+    if (pl.wide) return launch_fp8_gemm_tw(a, a_s, b, b_s, M, N, K, c, stream);
     if (pl.pair) return launch_fp8_gemm_tm(a, a_s, b, b_s, M, N, K, c, stream);
     CUtensorMap tp, tq, tc;
     memset(&tc, 0, sizeof(tc));
@@ -1098,6 +1124,34 @@ int launch_fp8_gemm_grouped(const void* table_dev, int n, const void* a, const f
         case 32: return launch_variant<32, true>(dummy, tq, dummy, prm, stream);
         default: return launch_variant<64, true>(dummy, tq, dummy, prm, stream);
     }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Self-test of the bounded wait the tcgen05 kernels are built on: one thread waits, with the given limit, for
+// an mbarrier phase that nothing will ever complete.  The wait runs out, records (kind 9, counter, CTA) in the
+// status words and the kernel returns normally: nothing traps, faults or spins without a bound.
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+__global__ void bounded_wait_selftest_kernel(unsigned int* status, uint64_t limit_ns) {
+    __shared__ uint64_t bar;
+    __shared__ Control ctl;
+    if (threadIdx.x == 0) {
+        ctl.abort_flag = 0;
+        mbar_init(smem_u32(&bar), 1);
+        mbar_fence_init();
+        (void)bounded_wait_ns(smem_u32(&bar), 0, &ctl, status, 9, 0, limit_ns);
+    }
+}
+
+}  // namespace
+
+int launch_bounded_wait_selftest(uint64_t limit_ns, cudaStream_t stream) {
+    unsigned int* status = status_device_ptr();
+    if (!status) return DSV3_ERR_CUDA;
+    bounded_wait_selftest_kernel<<<1, 32, 0, stream>>>(status, limit_ns);
+    DSV3_CUDA_TRY(cudaGetLastError());
+    return DSV3_OK;
 }
 
 }  // namespace dsv3

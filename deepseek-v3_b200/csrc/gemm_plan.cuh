@@ -12,6 +12,7 @@ struct TcPlan {
     int error;  // DSV3_OK, or the status to return (detail recorded): a pinned kernel / split factor that cannot be honoured
     bool swap;  // true: weights on the MMA M axis (small M)
     bool pair;  // token-major tiles on CTA pairs (fp8_gemm_tm.cu); never with split-K
+    bool wide;  // with pair: 256 x 256 tiles (fp8_gemm_tw.cu)
     int bn;     // rows of the second operand tile
     int tiles_p, tiles_q, splits, kc;
 };
@@ -36,6 +37,11 @@ bool tm_pair_supported(int64_t M, int64_t N, int64_t K, bool forced);
 int launch_fp8_gemm_tm(const void* a, const float* a_s, const void* b, const float* b_s, int64_t M, int64_t N,
                        int64_t K, void* c, cudaStream_t stream);
 
+// Token-major kernel on CTA pairs with 256-wide accumulators (256 x 256 tiles, no split-K): fp8_gemm_tw.cu.
+bool tw_pair_supported(int64_t M, int64_t N, int64_t K, bool forced);
+int launch_fp8_gemm_tw(const void* a, const float* a_s, const void* b, const float* b_s, int64_t M, int64_t N,
+                       int64_t K, void* c, cudaStream_t stream);
+
 // Decode-sized Linear without tcgen05 set-up (fp8_linear_small.cu): M <= 16; x != nullptr quantises bf16 activations
 // in the kernel's prologue (K % 128 == 0), otherwise (a, a_s) are the quantised activations (K % 16 == 0).
 bool small_linear_supported(const void* act, const void* w, const void* c, int64_t M, int64_t N, int64_t K, bool fused);
@@ -48,6 +54,9 @@ int build_group_table(void* table_dev, const void* const* weights, const float* 
                       int64_t K, cudaStream_t stream);
 int launch_fp8_gemm_grouped(const void* table_dev, int n, const void* a, const float* a_s, const int* seg_dev,
                             int64_t rows_total, int64_t rows_hint, int64_t N, int64_t K, void* c, cudaStream_t stream);
+
+// One thread waits for an mbarrier phase that never completes; the bounded wait gives up after limit_ns.
+int launch_bounded_wait_selftest(uint64_t limit_ns, cudaStream_t stream);
 
 // Kernel / split-K override set through dsv3_set_gemm_policy (0 = automatic).
 int gemm_policy_kernel();

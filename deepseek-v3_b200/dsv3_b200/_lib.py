@@ -25,7 +25,7 @@ EXPORTS = (
     "dsv3_fp8_gemm_workspace_bytes", "dsv3_fp8_gemm", "dsv3_set_gemm_policy", "dsv3_weight_quant",
     "dsv3_check_device_status", "dsv3_fp8_gemm_static", "dsv3_fp8_gemm_static_scratch_bytes",
     "dsv3_group_table_bytes", "dsv3_group_table_build", "dsv3_fp8_gemm_grouped", "dsv3_moe_combine", "dsv3_moe_route",
-    "dsv3_fp8_linear", "dsv3_swiglu_quant", "dsv3_p2p_handle_bytes", "dsv3_p2p_create", "dsv3_p2p_connect", "dsv3_p2p_connect_local", "dsv3_p2p_base",
+    "dsv3_fp8_linear", "dsv3_swiglu_quant", "dsv3_selftest_bounded_wait", "dsv3_p2p_handle_bytes", "dsv3_p2p_create", "dsv3_p2p_connect", "dsv3_p2p_connect_local", "dsv3_p2p_base",
     "dsv3_allreduce_oneshot", "dsv3_allreduce_oneshot_pair_on_one_gpu", "dsv3_p2p_destroy",
 )
 
@@ -48,6 +48,7 @@ def _load() -> ctypes.CDLL:
     lib.dsv3_strerror.restype = ctypes.c_char_p
     lib.dsv3_last_error.restype = ctypes.c_char_p
     lib.dsv3_act_quant.argtypes = [vp, i64, i64, ci, ci, vp, vp, vp]
+    lib.dsv3_selftest_bounded_wait.argtypes = [ctypes.c_uint64, vp]
     lib.dsv3_swiglu_quant.argtypes = [vp, vp, i64, i64, ci, vp, vp, vp]
     lib.dsv3_weight_dequant.argtypes = [vp, vp, i64, i64, ci, vp, vp]
     lib.dsv3_fp8_gemm_workspace_bytes.argtypes = [i64, i64, i64]

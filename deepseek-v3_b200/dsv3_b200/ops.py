@@ -16,6 +16,7 @@ from . import _lib
 from ._lib import lib
 
 KERNEL_AUTO, KERNEL_CUDA_CORE, KERNEL_TC_TOKEN_MAJOR, KERNEL_TC_WEIGHT_MAJOR, KERNEL_TC_TOKEN_PAIR, KERNEL_DECODE = 0, 1, 2, 3, 4, 5
+KERNEL_TC_TOKEN_PAIR_WIDE = 6
 
 _workspaces: Dict[Tuple[int, int], torch.Tensor] = {}
 

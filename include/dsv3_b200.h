@@ -137,7 +137,8 @@ int dsv3_fp8_gemm_static(const void* a, const float* a_s, const void* b, const f
  *   2 = tcgen05 kernel, tokens on the MMA M axis, one CTA per 128 x 128 tile,
  *   3 = tcgen05 kernel, weights on the MMA M axis (small M),
  *   4 = tcgen05 kernel, tokens on the MMA M axis, CTA pairs on 256 x 128 tiles (needs M > 128, no split-K),
- *   5 = decode kernel (warp-level FP8 MMA on weights streamed through registers; needs M <= 16).
+ *   5 = decode kernel (warp-level FP8 MMA on weights streamed through registers; needs M <= 16),
+ *   6 = tcgen05 kernel, tokens on the MMA M axis, CTA pairs on 256 x 256 tiles (needs M > 128, N > 128, no split-K).
  * split_k = 0 lets the library choose.  A pinned kernel or split factor is honoured or the GEMM call fails
  * with DSV3_ERR_UNSUPPORTED (shape the kernel cannot take, split factor that does not fit); it is never
  * silently replaced.  The setting is one process-wide pair of integers read by every later dsv3_fp8_gemm /
@@ -239,6 +240,15 @@ int dsv3_weight_quant(const void* w, int64_t N, int64_t K, void* q, float* s, ds
  * and clears the word; `detail` (may be NULL) receives 4 words describing the wait.
  */
 int dsv3_check_device_status(dsv3_stream_t stream, uint32_t detail[4]);
+
+/*
+ * Self-test of the bounded device-side wait: enqueues a one-thread kernel that waits for an mbarrier phase nothing
+ * completes; after limit_ns (1 ns .. 1 s) the wait gives up and records kind 9 in the status words, so the next
+ * dsv3_check_device_status returns DSV3_ERR_DEVICE_TIMEOUT.  The kernel returns normally; nothing faults or traps.
+ * Callers of the GEMM entry points should poll dsv3_check_device_status at step boundaries: after a give-up the
+ * affected result is incomplete.
+ */
+int dsv3_selftest_bounded_wait(uint64_t limit_ns, dsv3_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -15,7 +15,7 @@ from gpu_util import bf16_bits, assert_gemm_close
 
 pytestmark = pytest.mark.gpu
 
-AUTO, CORE, TC_TOKEN, TC_WEIGHT, TC_PAIR = 0, 1, 2, 3, 4
+AUTO, CORE, TC_TOKEN, TC_WEIGHT, TC_PAIR, TC_WIDE = 0, 1, 2, 3, 4, 6
 
 
 @pytest.fixture(scope="module")
@@ -70,27 +70,29 @@ SMALL = [  # (M, N, K, seed)
 ]
 
 
-def refusal(policy, split, M, Kd):
+def refusal(policy, split, M, Kd, N=1 << 20):
     """Why the library must refuse this pinned (kernel, split factor), or None.  Pinned values are honoured or
     refused, never silently replaced."""
     kc = -(-Kd // 128)
     if split > kc:
         return "pinned split factor"
-    if policy == TC_PAIR and M <= 128:
-        return "more than 128 tokens"
-    if policy == TC_PAIR and split > 1:
+    if policy in (TC_PAIR, TC_WIDE) and split > 1:
         return "pinned split factor"
+    if policy in (TC_PAIR, TC_WIDE) and M <= 128:
+        return "more than 128 tokens"
+    if policy == TC_WIDE and N <= 128:
+        return "more than 128 weight rows"
     return None
 
 
 @pytest.mark.parametrize("policy,split", [(CORE, 0), (TC_TOKEN, 1), (TC_WEIGHT, 1), (TC_TOKEN, 2), (TC_WEIGHT, 3),
-                                          (TC_PAIR, 0), (AUTO, 0)],
-                         ids=["core", "tctoken", "tcweight", "tctoken_split2", "tcweight_split3", "tcpair", "auto"])
+                                          (TC_PAIR, 0), (TC_WIDE, 0), (AUTO, 0)],
+                         ids=["core", "tctoken", "tcweight", "tctoken_split2", "tcweight_split3", "tcpair", "tcwide", "auto"])
 @pytest.mark.parametrize("M,N,Kd,seed", SMALL)
 def test_fp8_gemm_vs_oracle(K, policy, split, M, N, Kd, seed):
     import dsv3_b200
     xq, xs, wq, ws = quantised_case(M, N, Kd, seed)
-    why = refusal(policy, split, M, Kd)
+    why = refusal(policy, split, M, Kd, N)
     if why is not None:
         with pytest.raises(dsv3_b200.Dsv3Error, match=why) as e:
             run(K, policy, split, xq, xs, wq, ws)
@@ -102,8 +104,10 @@ def test_fp8_gemm_vs_oracle(K, policy, split, M, N, Kd, seed):
     assert_gemm_close(y, ref)
 
 
-PAIR = [  # shapes for the CTA-pair kernel: (M, N, K, seed)
+PAIR = [  # shapes for the CTA-pair kernels: (M, N, K, seed)
     (129, 128, 128, 60),      # second CTA of the only pair has one valid token row; a single K chunk
+    (129, 129, 128, 66),      # 256-wide tiles: one valid column in the right half
+    (513, 2052, 640, 67),     # 256-wide tiles: the last tile's right half lies wholly beyond N
     (300, 520, 896, 61),      # odd number of token tiles (the last pair's second tile is empty), odd number of K chunks
     (256, 1000, 1152, 62),    # N % 8 != 0 would forbid the tensor-map store: 1000 is fine, see next
     (257, 1001, 384, 63),     # N % 8 != 0: plain stores; three token tiles
@@ -123,6 +127,10 @@ def test_fp8_gemm_cta_pair_kernel_vs_oracle_and_single_cta_kernel(K, M, N, Kd, s
     assert np.array_equal(bf16_bits(y), bf16_bits(y1))
     # twice in a row on a warm pipeline
     assert np.array_equal(bf16_bits(run(K, TC_PAIR, 0, xq, xs, wq, ws)), bf16_bits(y))
+    if N > 128:     # 256 x 256 pair tiles: the same again
+        yw = run(K, TC_WIDE, 0, xq, xs, wq, ws)
+        assert np.array_equal(bf16_bits(yw), bf16_bits(y))
+        assert np.array_equal(bf16_bits(run(K, TC_WIDE, 0, xq, xs, wq, ws)), bf16_bits(y))
 
 
 def test_fp8_gemm_unaligned_k_uses_cuda_core_kernel(K):
@@ -255,7 +263,7 @@ def test_fp8_gemm_matches_gpu_reference_goldens_at_v3_shapes(K, golden_gpu, name
     assert hashlib.sha256(xq.cpu().view(torch.uint8).numpy().tobytes()).hexdigest() == str(golden_gpu[f"{name}.act_quant.y.sha"])
     assert hashlib.sha256(xs.cpu().numpy().tobytes()).hexdigest() == str(golden_gpu[f"{name}.act_quant.s.sha"])
     head = torch.from_numpy(golden_gpu[f"{name}.fp8_gemm.c.head"].view(np.int16)).view(torch.bfloat16).float()
-    policies = [(AUTO, 0), (CORE, 0)] + ([(TC_WEIGHT, 0)] if M <= 64 else [(TC_TOKEN, 1), (TC_PAIR, 0)])
+    policies = [(AUTO, 0), (CORE, 0)] + ([(TC_WEIGHT, 0)] if M <= 64 else [(TC_TOKEN, 1), (TC_PAIR, 0), (TC_WIDE, 0)])
     for policy, split in policies:
         y = run(K, policy, split, xq, xs, wq, ws)
         got = y.reshape(-1)[:head.numel()].float().cpu()
@@ -301,12 +309,31 @@ def test_fp8_gemm_full_size_properties(K, M, N, Kd, seed):
     dsv3_b200.set_gemm_policy(AUTO, 0)
     y3 = K.fp8_gemm(xq, xs * 2, wq, ws)
     assert torch.equal(y3.float(), y.float() * 2)
-    # (4) the token-major tcgen05 kernels (one CTA per tile, CTA pairs) agree bit for bit, whichever was chosen above
+    # (4) the token-major tcgen05 kernels (one CTA per tile, CTA pairs on 128- and 256-wide tiles) agree bit for bit, whichever was chosen above
     if M > 128:
         dsv3_b200.set_gemm_policy(TC_TOKEN, 1)
         y4 = K.fp8_gemm(xq, xs, wq, ws)
         dsv3_b200.set_gemm_policy(TC_PAIR, 0)
         y5 = K.fp8_gemm(xq, xs, wq, ws)
         assert torch.equal(y4, y5)
+        dsv3_b200.set_gemm_policy(TC_WIDE, 0)
+        assert torch.equal(y4, K.fp8_gemm(xq, xs, wq, ws))
         err = (y4.float() - y2.float()).abs()
         assert bool((err <= 1e-2 * (y2.float().abs() + rms)).all())
+
+
+def test_bounded_wait_gives_up_and_reports_through_the_status_words():
+    """The give-up path of the mbarrier waits in the tcgen05 kernels: a wait on a barrier nobody arrives at runs out
+    after its limit (2 ms), the kernel returns, the host reads DSV3_ERR_DEVICE_TIMEOUT and the cleared status."""
+    import ctypes
+    import dsv3_b200
+    from dsv3_b200 import _lib
+    st = torch.cuda.current_stream().cuda_stream
+    _lib.check(_lib.lib.dsv3_selftest_bounded_wait(2_000_000, st))
+    torch.cuda.synchronize()
+    detail = (ctypes.c_uint32 * 4)()
+    assert _lib.lib.dsv3_check_device_status(st, detail) == _lib.ERR_DEVICE_TIMEOUT
+    assert detail[1] == 9
+    dsv3_b200.check_device_status()          # clean again
+    with pytest.raises(_lib.Dsv3Error):
+        _lib.check(_lib.lib.dsv3_selftest_bounded_wait(0, st))
