@@ -18,10 +18,11 @@
 //                     tile's 256 weight rows), five stages.  Both producers' loads complete on the LEADER's full[]
 //                     barrier (ordinary, non-multicast loads; only the completion signal crosses to the peer),
 //                     each waits on its own empty[].
-//   warp 1 (1 lane)   leader only: MMA issuer.  Per chunk g: wait full[stage], wait tempty[g & 1] (16 arrivals: the
-//                     promotion warps of both CTAs), 4 x tcgen05.mma.cta_group::2 kind::f8f6f4 (M256 N256 K32),
-//                     commit -> tfull[g & 1] and empty[stage] of both CTAs.  This one thread waits for every phase
-//                     of every barrier it uses.
+//   warps 1,2 (1 lane each)  leader only: MMA issuers; chunk g belongs to issuer g % 2, which owns TMEM slot g % 2.
+//                     Per chunk: wait full[stage], wait tempty[slot] (16 arrivals: the promotion warps of both CTAs),
+//                     4 x tcgen05.mma.cta_group::2 kind::f8f6f4 (M256 N256 K32), commit -> tfull[slot] and
+//                     empty[stage] of both CTAs.  Stages alternate between the issuers, so full[] is waited for
+//                     without a probe.
 //   warps 4..11       promotion of this CTA's 128 x 256 half: warps 4..7 own columns 0..127 (one b_s block), warps
 //                     8..11 columns 128..255; a thread owns one accumulator row.  A chunk product is read back in
 //                     four pieces of 32 columns into two alternating buffers: while the tcgen05.ld of one piece is
@@ -45,27 +46,36 @@ namespace dsv3 {
 
 namespace {
 
-constexpr int kNumThreads = 384;          // warp 0: TMA producer, warp 1: MMA issuer (leader), 2-3 idle, 4..11: promotion
+constexpr int kNumThreads = 384;          // warp 0: TMA producer, warps 1-2: MMA issuers (leader), 3 idle, 4..11: promotion
 constexpr int kFirstPromoWarp = 4;
 constexpr int kPromoThreads = 256;
 constexpr int kRegsControl = 40;
 constexpr int kRegsPromo = 232;
+// setmaxnreg.inc waits for registers of the CTA's pool, which is what the launch allocated (168 per thread, the
+// most 384 threads can have): the two budgets must fit into it or the promotion warps would wait forever.
 static_assert(128 * kRegsControl + 256 * kRegsPromo <= 384 * 168, "register pool");
 
 constexpr int kBN = 256;                              // tile width: two b_s blocks, one per promotion warp group
 constexpr int kBHalf = kBN / 2;                       // weight rows each CTA of the pair loads
 constexpr int kChunkBytes = (kPRows + kBHalf) * kChunk;   // per CTA: token tile + half weight tile of one chunk
-constexpr int kStages = 5;                            // of one chunk each
+constexpr int kStorePasses = 1;                       // result tile staged whole (1) or one 64-column box per warp group at a time (2)
+constexpr int kStages = kStorePasses == 1 ? 5 : 6;    // of one chunk each
 constexpr int kSlots = 2;                             // TMEM slots of one chunk product (256 columns) each
 constexpr int kTmemCols = kSlots * kBN;
 constexpr int kPiece = 32;                            // columns per read-back
 constexpr int kPieces = 128 / kPiece;                 // read-backs per chunk product and thread
 static_assert(kPieces % 2 == 0, "a chunk's first piece goes to buffer 0 while buffer 1 holds the last piece of the chunk before");
-constexpr int kStoreBytes = kPRows * kBN * 2;         // bf16 result tile, four 128-byte-swizzled 128 x 64 boxes
+constexpr int kStoreBytes = kPRows * kBN * 2 / kStorePasses;   // bf16 result tile: 128-byte-swizzled 128 x 64 boxes
 constexpr int kSmemBytes = kStages * kChunkBytes + kStoreBytes + 1024 + 1024;
 static_assert(kSmemBytes <= 232448, "shared memory per CTA");
 static_assert(kSmemBytes > 116 * 1024, "one CTA per SM (it allocates all of TMEM)");
 static_assert(kTmemCols == 512, "all of TMEM");
+// The issuers alternate, so a stage's full[] barrier is waited for by one issuer at one use and by the other at the
+// next.  A parity wait is only exact for a barrier that is at most one phase behind.  That holds here: an issuer
+// reaches chunk g after it was given its TMEM slot for chunk g - 2, i.e. after the promotion warps have read chunk
+// g - 4 and, in order, every chunk before it -- among them chunk g - kStages, the stage's previous use, whose
+// product could only exist after the other issuer had waited for that use's loads.
+static_assert(kStages >= 4 && kSlots == 2, "phase argument for the full[] waits of alternating issuers");
 static_assert((kPRows * kChunk) % 1024 == 0 && kChunkBytes % 1024 == 0, "operand tiles keep the swizzle atom's alignment");
 
 struct TwParams {
@@ -116,7 +126,7 @@ fp8_gemm_tw_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     auto tfull_bar = [&](int s) { return bar0 + 8u * (2 * kStages + s); };
     auto tempty_bar = [&](int s) { return bar0 + 8u * (2 * kStages + kSlots + s); };   // used in the leader only
 
-    const int warp = threadIdx.x >> 5;
+    const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);   // uniform, and known to be
     const int lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();            // 0: leader (issues the MMAs), 1: peer
     const int pair = static_cast<int>(blockIdx.x >> 1);
@@ -189,37 +199,46 @@ fp8_gemm_tw_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                 for (uint32_t d = (g > kStages ? g - kStages : 0u); ok && d < g; ++d)
                     ok = bounded_wait(empty_bar(d % kStages), (d / kStages) & 1u, ctl, p.status, 1, d);
             }
-        } else if (warp == 1) {
-            // ------------------------------------------------------------ MMA issuer (leader CTA)
-            if (lane == 0 && rank == 0) {
+        } else if (warp <= 2) {
+            // ------------------------------------------------------------ MMA issuers (leader CTA; chunk g -> issuer g % 2)
+            // One thread issues about one tcgen05 instruction per hundred cycles, and a chunk costs eight (four MMAs,
+            // four commits) for 512 tensor-core cycles: two threads share the chunks, each owning one TMEM slot.
+            // The whole warp walks the loop (waits included) and one elected lane issues: control flow, addresses
+            // and descriptors then stay warp-uniform, which is what makes a tcgen05 instruction cheap to issue.
+            if (rank == 0) {
                 constexpr uint32_t idesc = umma_idesc_e4m3_f32(2 * kPRows, kBN);
-                const uint32_t peer_tfull0 = mapa_shared(tfull_bar(0), 1);
+                const uint32_t me = static_cast<uint32_t>(warp - 1);
+                const int slot = static_cast<int>(me);
+                const uint32_t peer_tfull = mapa_shared(tfull_bar(slot), 1);
                 const uint32_t peer_empty0 = mapa_shared(empty_bar(0), 1);
+                const uint32_t d_tmem = tmem_base + slot * kBN;
                 bool ok = true;
                 uint32_t g = 0;
                 for (int tile = pair; ok && tile < p.num_tiles; tile += n_pairs) {
                     for (int k = 0; k < kc; ++k, ++g) {
+                        if ((g & 1u) != me) continue;
                         const int s = g % kStages;
-                        const int slot = static_cast<int>(g & 1u);
-                        ok = bounded_wait(full_bar(s), (g / kStages) & 1u, ctl, p.status, 2, g);
+                        ok = __all_sync(0xffffffffu, bounded_wait(full_bar(s), (g / kStages) & 1u, ctl, p.status, 2, g));
                         if (!ok) break;
-                        ok = bounded_wait(tempty_bar(slot), ((g >> 1) & 1u) ^ 1u, ctl, p.status, 3, g);
+                        ok = __all_sync(0xffffffffu, bounded_wait(tempty_bar(slot), ((g >> 1) & 1u) ^ 1u, ctl, p.status, 3, g));
                         if (!ok) break;
                         tc_fence_after();
                         const uint32_t sp = tiles + s * kChunkBytes;
                         const uint64_t da = umma_desc_k_major_sw128(sp);
                         const uint64_t db = umma_desc_k_major_sw128(sp + kPRows * kChunk);
-                        const uint32_t d_tmem = tmem_base + slot * kBN;
-    #pragma unroll
-                        for (int kk = 0; kk < kChunk / 32; ++kk) {
-                            // 32 bytes further along K inside the 128-byte swizzle atom: +2 in address units of 16 B
-                            tc_mma_f8_pair(d_tmem, da + 2u * kk, db + 2u * kk, idesc, kk > 0 ? 1u : 0u);
+                        if (elect_one()) {
+#pragma unroll
+                            for (int kk = 0; kk < kChunk / 32; ++kk) {
+                                // 32 bytes further along K inside the 128-byte swizzle atom: +2 in address units of 16 B
+                                tc_mma_f8_pair(d_tmem, da + 2u * kk, db + 2u * kk, idesc, kk > 0 ? 1u : 0u);
+                            }
+                            // this chunk's product is complete in the TMEM of both CTAs; the stage is reusable in both
+                            tc_commit_pair(tfull_bar(slot));
+                            tc_commit_pair(peer_tfull);
+                            tc_commit_pair(empty_bar(s));
+                            tc_commit_pair(peer_empty0 + 8u * s);
                         }
-                        // this chunk's product is complete in the TMEM of both CTAs; the stage is reusable in both
-                        tc_commit_pair(tfull_bar(slot));
-                        tc_commit_pair(peer_tfull0 + 8u * slot);
-                        tc_commit_pair(empty_bar(s));
-                        tc_commit_pair(peer_empty0 + 8u * s);
+                        __syncwarp();
                     }
                 }
             }
@@ -265,22 +284,30 @@ fp8_gemm_tw_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             const int64_t n0 = static_cast<int64_t>(tq) * kBN + col0;
             if (n0 >= p.N) return;                                    // the tile's right half lies beyond N
             if (p.tma_store) {
-                uint8_t* sbuf = store_buf + half * (2 * kPRows * 128);
-                const bool issuer = ((threadIdx.x & 127) == 0);
-                if (issuer) bulk_wait_group_read0();
-                asm volatile("bar.sync %0, 128;" ::"r"(2 + half) : "memory");
+                constexpr int kBoxes = 2 / kStorePasses;               // boxes per warp group and pass
+                uint8_t* sbuf = store_buf + half * (kBoxes * kPRows * 128);
+                const bool issuer = (((threadIdx.x - kFirstPromoWarp * 32) & 127) == 0);
 #pragma unroll
-                for (int cc = 0; cc < 16; ++cc) {      // 16-byte slot cc of the thread's 128 columns: box cc / 8, slot cc % 8
-                    const uint4 o = make_uint4(pack_bf16x2(acc[4 * cc].x, acc[4 * cc].y), pack_bf16x2(acc[4 * cc + 1].x, acc[4 * cc + 1].y),
-                                               pack_bf16x2(acc[4 * cc + 2].x, acc[4 * cc + 2].y), pack_bf16x2(acc[4 * cc + 3].x, acc[4 * cc + 3].y));
-                    *reinterpret_cast<uint4*>(sbuf + (cc >> 3) * (kPRows * 128) + row * 128 + (((cc & 7) ^ (row & 7)) << 4)) = o;
-                }
-                fence_proxy_async_shared();
-                asm volatile("bar.sync %0, 128;" ::"r"(2 + half) : "memory");
-                if (issuer) {
-                    tma_store_2d(&tmap_c, smem_u32(sbuf), static_cast<int>(n0), tp * kPRows);
-                    if (n0 + 64 < p.N) tma_store_2d(&tmap_c, smem_u32(sbuf + kPRows * 128), static_cast<int>(n0) + 64, tp * kPRows);
-                    bulk_commit_group();
+                for (int pass = 0; pass < kStorePasses; ++pass) {
+                    if (issuer) bulk_wait_group_read0();
+                    asm volatile("bar.sync %0, 128;" ::"r"(2 + half) : "memory");
+#pragma unroll
+                    for (int c8 = 0; c8 < 8 * kBoxes; ++c8) {      // 16-byte slot of the thread's columns: box cc / 8, slot cc % 8
+                        const int cc = pass * 8 * kBoxes + c8;
+                        const uint4 o = make_uint4(pack_bf16x2(acc[4 * cc].x, acc[4 * cc].y), pack_bf16x2(acc[4 * cc + 1].x, acc[4 * cc + 1].y),
+                                                   pack_bf16x2(acc[4 * cc + 2].x, acc[4 * cc + 2].y), pack_bf16x2(acc[4 * cc + 3].x, acc[4 * cc + 3].y));
+                        *reinterpret_cast<uint4*>(sbuf + (c8 >> 3) * (kPRows * 128) + row * 128 + (((c8 & 7) ^ (row & 7)) << 4)) = o;
+                    }
+                    fence_proxy_async_shared();
+                    asm volatile("bar.sync %0, 128;" ::"r"(2 + half) : "memory");
+                    if (issuer) {
+#pragma unroll
+                        for (int bx = 0; bx < kBoxes; ++bx) {
+                            const int64_t n = n0 + (pass * kBoxes + bx) * 64;
+                            if (n < p.N) tma_store_2d(&tmap_c, smem_u32(sbuf + bx * (kPRows * 128)), static_cast<int>(n), tp * kPRows);
+                        }
+                        bulk_commit_group();
+                    }
                 }
             } else {
                 const int64_t m = static_cast<int64_t>(tp) * kPRows + row;
@@ -296,55 +323,47 @@ fp8_gemm_tw_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             }
         };
 
-        // Scale rows of a tile for this thread: a_s of its token (clamped at the edge), b_s of the weight block of
-        // its column half (clamped where that half lies beyond N).
-        struct Scales {
-            const float* as_ptr;
-            const float* bs_ptr;
-            float first;          // product of the scales of the tile's first chunk
-        };
-        auto tile_scales = [&](const Tile& t) {
+        // Scale rows of a tile for this thread, as element offsets: a_s of its token (clamped at the edge), b_s of
+        // the weight block of its column half (clamped where that half lies beyond N).
+        auto as_row = [&](const Tile& t) {
             const int64_t tok = static_cast<int64_t>(2 * t.pp + static_cast<int>(rank)) * kPRows + row;
-            Scales sc;
-            sc.as_ptr = p.a_s + min(tok, p.M - 1) * kc;
-            sc.bs_ptr = p.b_s + static_cast<int64_t>(min(2 * t.q + half, p.nblk - 1)) * kc;
-            sc.first = __ldg(sc.as_ptr) * __ldg(sc.bs_ptr);
-            return sc;
+            return p.a_s + min(tok, p.M - 1) * kc;
         };
+        auto bs_row = [&](const Tile& t) { return p.b_s + static_cast<int64_t>(min(2 * t.q + half, p.nblk - 1)) * kc; };
 
         bool ok = true;
         uint32_t g = 0;            // chunk counter
         int tile = pair;
         if (tile < p.num_tiles) {
             Tile cur = decode_tile(tile, p);
-            Scales cs = tile_scales(cur);
+            float first = __ldg(as_row(cur)) * __ldg(bs_row(cur));     // product of the scales of the tile's first chunk
             while (true) {
-                float sc = cs.first;
-                float pend_sc = 0.0f;      // scale of the chunk whose last piece waits in v[1] (first chunk: zeros)
+                const float* as_ptr = as_row(cur);
+                const float* bs_ptr = bs_row(cur);
+                float sc = first;
 #pragma unroll
                 for (int j = 0; j < 64; ++j) acc[j] = make_float2(0.0f, 0.0f);
-#pragma unroll
-                for (int j = 0; j < kPiece; ++j) v[1][j] = 0u;
                 for (int k = 0; k < kc; ++k, ++g) {
                     const int slot = static_cast<int>(g & 1u);
-                    const bool mine = bounded_wait(tfull_bar(slot), (g >> 1) & 1u, ctl, p.status, 4, g);
-                    if (!__all_sync(0xffffffffu, mine)) { ok = false; break; }
+                    const bool mine = bounded_wait_lean(tfull_bar(slot), (g >> 1) & 1u, ctl, p.status, 4, g);
+                    ok = __all_sync(0xffffffffu, mine);
+                    if (!ok) break;
                     tc_fence_after();
                     const uint32_t t_slot = t_lane + slot * kBN;
-                    load_piece(t_slot, v[0]);
+                    // The left 64 columns are read back and folded, then the right 64 are read back and the slot
+                    // returns to the issuer: two read-back latencies per chunk; the last fold follows the release.
+                    tc_ld_x64(t_slot, &v[0][0]);
                     // product of the scales of the tile's next chunk, one chunk ahead (clamped: the last re-reads its own)
                     const int kn = min(k + 1, kc - 1);
-                    const float sc_next = __ldg(cs.as_ptr + kn) * __ldg(cs.bs_ptr + kn);
-                    fold(v[1], pend_sc, kPieces - 1);      // last piece of the chunk before, under this chunk's first load
+                    const float sc_next = __ldg(as_ptr + kn) * __ldg(bs_ptr + kn);
                     tc_wait_ld();
-#pragma unroll
-                    for (int pc = 1; pc < kPieces; ++pc) {
-                        load_piece(t_slot + pc * kPiece, v[pc & 1]);
-                        fold(v[(pc - 1) & 1], sc, pc - 1);
-                        tc_wait_ld();
-                    }
+                    fold(v[0], sc, 0);
+                    fold(v[1], sc, 1);
+                    tc_ld_x64(t_slot + 2 * kPiece, &v[0][0]);
+                    tc_wait_ld();
                     release(slot);
-                    pend_sc = sc;
+                    fold(v[0], sc, 2);
+                    fold(v[1], sc, 3);
                     sc = sc_next;
                 }
                 if (!ok) break;
@@ -353,23 +372,20 @@ fp8_gemm_tw_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                 const int next = tile + n_pairs;
                 const bool more = next < p.num_tiles;
                 Tile nt = cur;
-                Scales ns = cs;
                 if (more) {
                     nt = decode_tile(next, p);
-                    ns = tile_scales(nt);
+                    first = __ldg(as_row(nt)) * __ldg(bs_row(nt));
                 }
-                fold(v[1], pend_sc, kPieces - 1);
                 write_tile(2 * cur.pp + static_cast<int>(rank), cur.q);
                 if (!more) break;
                 tile = next;
                 cur = nt;
-                cs = ns;
             }
         }
     }
 
     // ---------------------------------------------------------------- teardown
-    if (warp >= kFirstPromoWarp && (threadIdx.x & 127) == 0) bulk_wait_group0();   // result tiles have left shared memory
+    if (warp >= kFirstPromoWarp && ((threadIdx.x - kFirstPromoWarp * 32) & 127) == 0) bulk_wait_group0();   // result tiles have left shared memory
     __syncwarp();
     tc_fence_before();
     __syncthreads();

@@ -49,6 +49,26 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, Cont
     return bounded_wait_ns(bar, parity, ctl, status, what, g, kWaitLimitNs);
 }
 
+// The same wait for loops that are short of registers (the promotion loop of the 256-wide kernel): bounded by a
+// poll count instead of the clock, so that the only state is one counter.  A failed try_wait suspends the thread for
+// a hardware-defined time before it reports back, which makes the bound a matter of seconds.
+constexpr uint32_t kWaitLimitPolls = 1u << 22;
+__device__ __forceinline__ bool bounded_wait_lean(uint32_t bar, uint32_t parity, Control* ctl, unsigned int* status,
+                                                  uint32_t what, uint32_t g) {
+#pragma unroll 1
+    for (uint32_t spins = 0; spins < kWaitLimitPolls; ++spins) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spins & 1023u) == 1023u && ctl->abort_flag) return false;
+    }
+    ctl->abort_flag = 1;
+    if (atomicCAS(&status[0], 0u, 1u) == 0u) {
+        status[1] = what;
+        status[2] = g;
+        status[3] = blockIdx.x;
+    }
+    return false;
+}
+
 // bounded_wait preceded by the result of an earlier probe of the same barrier and parity.
 //
 // A parity probe (mbarrier.test_wait.parity P) answers "has the phase with parity P completed?", which is
