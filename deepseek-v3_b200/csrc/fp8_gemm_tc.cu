@@ -233,7 +233,7 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
     const uint32_t tab_ready_bar = bar0 + 8u * (2 * NS + 2 * NT);       // scale table of the item is filled
     const uint32_t tab_free_bar = bar0 + 8u * (2 * NS + 2 * NT + 1);    // scale table may be overwritten
 
-    const int warp = threadIdx.x >> 5;
+    const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);   // uniform, and known to be
     const int lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
@@ -302,7 +302,9 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
-        if (lane == 0) {
+        // The whole warp walks the loop (waits included) and one elected lane issues: control flow, addresses and
+        // descriptors then stay warp-uniform, which is what makes TMA and tcgen05 instructions cheap to issue.
+        {
             uint32_t g = 0;
             uint32_t probe = 0;   // result of try_wait on empty[] for chunk g, issued one chunk earlier
             bool ok = true;
@@ -315,27 +317,31 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
                 const int n_units = (it.c1 - it.c0 + UC - 1) / UC;
                 for (int u = 0; u < n_units; ++u, ++g) {
                     const int s = g % NS;
-                    ok = wait_probed(probe, empty_bar(s), ((g / NS) & 1u) ^ 1u, ctl, p.status, 1, g);
+                    ok = __all_sync(0xffffffffu, wait_probed(probe, empty_bar(s), ((g / NS) & 1u) ^ 1u, ctl, p.status, 1, g));
                     if (!ok) break;
                     probe = mbar_test_wait(empty_bar((g + 1) % NS), (((g + 1) / NS) & 1u) ^ 1u) ? 1u : 0u;
                     const int k0 = it.c0 + u * UC;
                     const int nch = min(UC, it.c1 - k0);
-                    mbar_arrive_expect_tx(full_bar(s), nch * C::kChunkBytes);
-                    for (int j = 0; j < nch; ++j) {
-                        const uint32_t dst = tiles + s * C::kStageBytes + j * C::kChunkBytes;
-                        tma_load_2d(dst, map_p, (k0 + j) * kChunk, p_row, full_bar(s));
-                        tma_load_2d(dst + kPRows * kChunk, &tmap_q, (k0 + j) * kChunk, q_row, full_bar(s));
+                    if (elect_one()) {
+                        mbar_arrive_expect_tx(full_bar(s), nch * C::kChunkBytes);
+                        for (int j = 0; j < nch; ++j) {
+                            const uint32_t dst = tiles + s * C::kStageBytes + j * C::kChunkBytes;
+                            tma_load_2d(dst, map_p, (k0 + j) * kChunk, p_row, full_bar(s));
+                            tma_load_2d(dst + kPRows * kChunk, &tmap_q, (k0 + j) * kChunk, q_row, full_bar(s));
+                        }
                     }
+                    __syncwarp();
                 }
             }
             // Nothing waits for the commits onto the empty[] barriers of the last units; wait for them here so
             // that none is in flight when the CTA leaves (it would land in whatever CTA gets this shared memory next).
             for (uint32_t d = (g > static_cast<uint32_t>(NS) ? g - NS : 0u); ok && d < g; ++d)
-                ok = bounded_wait(empty_bar(d % NS), (d / NS) & 1u, ctl, p.status, 1, d);
+                ok = __all_sync(0xffffffffu, bounded_wait(empty_bar(d % NS), (d / NS) & 1u, ctl, p.status, 1, d));
         }
     } else if (warp <= kIssuers) {
         // ------------------------------------------------------------ MMA issuers (chunk g -> issuer g % kIssuers)
-        if (lane == 0) {
+        // (converged warp, elected lane: see the producer)
+        {
             constexpr uint32_t idesc = umma_idesc_e4m3_f32(kPRows, BN);
             const uint32_t me = static_cast<uint32_t>(warp - 1);
             uint32_t g = 0;
@@ -348,8 +354,8 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
                     if (g % kIssuers != me) continue;
                     const int s = g % NS, ts = g % NT;
                     constexpr bool kProbeFull = (NS % kIssuers) == 0;
-                    ok = wait_probed(probe_t, tempty_bar(ts), ((g / NT) & 1u) ^ 1u, ctl, p.status, 3, g) &&
-                         wait_probed(kProbeFull ? probe_f : 0u, full_bar(s), (g / NS) & 1u, ctl, p.status, 2, g);
+                    ok = __all_sync(0xffffffffu, wait_probed(probe_t, tempty_bar(ts), ((g / NT) & 1u) ^ 1u, ctl, p.status, 3, g) &&
+                                                 wait_probed(kProbeFull ? probe_f : 0u, full_bar(s), (g / NS) & 1u, ctl, p.status, 2, g));
                     if (!ok) break;
                     {   // Probe the TMEM stage of this issuer's next unit now; the answer is read one iteration
                         // later.  A parity probe is only meaningful if the barrier's previous phase is known to be
@@ -363,19 +369,22 @@ fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_cons
                     }
                     tc_fence_after();
                     const int nch = min(UC, it.c1 - it.c0 - u * UC);
-                    for (int j = 0; j < nch; ++j) {
-                        const uint32_t sp = tiles + s * C::kStageBytes + j * C::kChunkBytes;
-                        const uint64_t dp = umma_desc_k_major_sw128(sp);
-                        const uint64_t dq = umma_desc_k_major_sw128(sp + kPRows * kChunk);
-                        const uint32_t d_tmem = tmem_base + (ts * UC + j) * BN;   // one TMEM region per chunk
+                    if (elect_one()) {
+                        for (int j = 0; j < nch; ++j) {
+                            const uint32_t sp = tiles + s * C::kStageBytes + j * C::kChunkBytes;
+                            const uint64_t dp = umma_desc_k_major_sw128(sp);
+                            const uint64_t dq = umma_desc_k_major_sw128(sp + kPRows * kChunk);
+                            const uint32_t d_tmem = tmem_base + (ts * UC + j) * BN;   // one TMEM region per chunk
 #pragma unroll
-                        for (int k = 0; k < kChunk / 32; ++k) {
-                            // 32 bytes further along K inside the 128-byte swizzle atom: +2 in address units of 16 B
-                            tc_mma_f8(d_tmem, dp + 2u * k, dq + 2u * k, idesc, k > 0 ? 1u : 0u);
+                            for (int k = 0; k < kChunk / 32; ++k) {
+                                // 32 bytes further along K inside the 128-byte swizzle atom: +2 in address units of 16 B
+                                tc_mma_f8(d_tmem, dp + 2u * k, dq + 2u * k, idesc, k > 0 ? 1u : 0u);
+                            }
                         }
+                        tc_commit(empty_bar(s));   // smem stage reusable once these MMAs have read it
+                        tc_commit(tfull_bar(ts));  // the unit's chunk products are complete in TMEM
                     }
-                    tc_commit(empty_bar(s));   // smem stage reusable once these MMAs have read it
-                    tc_commit(tfull_bar(ts));  // the unit's chunk products are complete in TMEM
+                    __syncwarp();
                 }
             }
         }

@@ -123,7 +123,7 @@ fp8_gemm_tm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     auto tfull_bar = [&](int s) { return bar0 + 8u * (2 * kStages + s); };
     auto tempty_bar = [&](int s) { return bar0 + 8u * (2 * kStages + kSlots + s); };   // used in the leader only
 
-    const int warp = threadIdx.x >> 5;
+    const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);   // uniform, and known to be
     const int lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();            // 0: leader (issues the MMAs), 1: peer
     const int pair = static_cast<int>(blockIdx.x >> 1);
@@ -174,7 +174,9 @@ fp8_gemm_tm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer (both CTAs)
-        if (lane == 0) {
+        // The whole warp walks the loop (waits included) and one elected lane issues: control flow, addresses and
+        // descriptors then stay warp-uniform, which is what makes TMA and tcgen05 instructions cheap to issue.
+        {
             uint32_t g = 0;
             uint32_t probe = 0;   // result of test_wait on empty[] for unit g, issued one unit earlier
             bool ok = true;
@@ -184,7 +186,7 @@ fp8_gemm_tm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                 const int b_row = t.q * kBN + static_cast<int>(rank) * kBHalf;
                 for (int u = 0; u < n_units; ++u, ++g) {
                     const int s = g % kStages;
-                    ok = wait_probed(probe, empty_bar(s), ((g / kStages) & 1u) ^ 1u, ctl, p.status, 1, g);
+                    ok = __all_sync(0xffffffffu, wait_probed(probe, empty_bar(s), ((g / kStages) & 1u) ^ 1u, ctl, p.status, 1, g));
                     if (!ok) break;
                     probe = mbar_test_wait(empty_bar((g + 1) % kStages), (((g + 1) / kStages) & 1u) ^ 1u) ? 1u : 0u;
                     const int k0 = u * kUC;
@@ -192,22 +194,26 @@ fp8_gemm_tm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                     const uint32_t lead_full = mapa_shared(full_bar(s), 0);
                     // the leader's barrier expects the bytes of both CTAs; the peer's loads may complete on it
                     // before this arrive has been made (the phase cannot complete without it)
-                    if (rank == 0) mbar_arrive_expect_tx(full_bar(s), 2 * nch * kChunkBytes);
-                    for (int j = 0; j < nch; ++j) {
-                        const uint32_t dst = tiles + s * kStageBytes + j * kChunkBytes;
-                        tma_load_2d_pair(dst, &tmap_a, (k0 + j) * kChunk, a_row, lead_full);
-                        tma_load_2d_pair(dst + kPRows * kChunk, &tmap_b, (k0 + j) * kChunk, b_row, lead_full);
+                    if (elect_one()) {
+                        if (rank == 0) mbar_arrive_expect_tx(full_bar(s), 2 * nch * kChunkBytes);
+                        for (int j = 0; j < nch; ++j) {
+                            const uint32_t dst = tiles + s * kStageBytes + j * kChunkBytes;
+                            tma_load_2d_pair(dst, &tmap_a, (k0 + j) * kChunk, a_row, lead_full);
+                            tma_load_2d_pair(dst + kPRows * kChunk, &tmap_b, (k0 + j) * kChunk, b_row, lead_full);
+                        }
                     }
+                    __syncwarp();
                 }
             }
             // Nothing waits for the commits onto the empty[] barriers of the last units; wait for them here so
             // that none is in flight when the CTA leaves (it would land in whatever CTA gets this shared memory next).
             for (uint32_t d = (g > kStages ? g - kStages : 0u); ok && d < g; ++d)
-                ok = bounded_wait(empty_bar(d % kStages), (d / kStages) & 1u, ctl, p.status, 1, d);
+                ok = __all_sync(0xffffffffu, bounded_wait(empty_bar(d % kStages), (d / kStages) & 1u, ctl, p.status, 1, d));
         }
     } else if (warp <= 2) {
         // ------------------------------------------------------------ MMA issuers (leader CTA; unit g -> issuer g % 2)
-        if (lane == 0 && rank == 0) {
+        // (converged warp, elected lane: see the producer)
+        if (rank == 0) {
             constexpr uint32_t idesc = umma_idesc_e4m3_f32(2 * kPRows, kBN);
             const uint32_t me = static_cast<uint32_t>(warp - 1);
             const int slot0 = static_cast<int>(me) * kUC;
@@ -220,32 +226,38 @@ fp8_gemm_tm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                     const int s = g % kStages;
                     const uint32_t par = (g >> 1) & 1u;            // this issuer's use count of its slots, mod 2
                     const int nch = min(kUC, kc - u * kUC);
-                    ok = bounded_wait(full_bar(s), (g / kStages) & 1u, ctl, p.status, 2, g);
+                    ok = __all_sync(0xffffffffu, bounded_wait(full_bar(s), (g / kStages) & 1u, ctl, p.status, 2, g));
                     if (!ok) break;
 #pragma unroll
                     for (int j = 0; j < kUC; ++j) {
-                        ok = wait_probed(probe_t[j], tempty_bar(slot0 + j), par ^ 1u, ctl, p.status, 3, g);
+                        ok = __all_sync(0xffffffffu, wait_probed(probe_t[j], tempty_bar(slot0 + j), par ^ 1u, ctl, p.status, 3, g));
                         if (!ok) break;
                         tc_fence_after();
-                        if (j < nch) {
-                            const uint32_t sp = tiles + s * kStageBytes + j * kChunkBytes;
-                            const uint64_t da = umma_desc_k_major_sw128(sp);
-                            const uint64_t db = umma_desc_k_major_sw128(sp + kPRows * kChunk);
-                            const uint32_t d_tmem = tmem_base + (slot0 + j) * kBN;
+                        if (elect_one()) {
+                            if (j < nch) {
+                                const uint32_t sp = tiles + s * kStageBytes + j * kChunkBytes;
+                                const uint64_t da = umma_desc_k_major_sw128(sp);
+                                const uint64_t db = umma_desc_k_major_sw128(sp + kPRows * kChunk);
+                                const uint32_t d_tmem = tmem_base + (slot0 + j) * kBN;
 #pragma unroll
-                            for (int k = 0; k < kChunk / 32; ++k) {
-                                // 32 bytes further along K inside the 128-byte swizzle atom: +2 in address units of 16 B
-                                tc_mma_f8_pair(d_tmem, da + 2u * k, db + 2u * k, idesc, k > 0 ? 1u : 0u);
+                                for (int k = 0; k < kChunk / 32; ++k) {
+                                    // 32 bytes further along K inside the 128-byte swizzle atom: +2 in address units of 16 B
+                                    tc_mma_f8_pair(d_tmem, da + 2u * k, db + 2u * k, idesc, k > 0 ? 1u : 0u);
+                                }
                             }
+                            // this chunk's product is complete in the TMEM of both CTAs
+                            tc_commit_pair(tfull_bar(slot0 + j));
+                            tc_commit_pair(mapa_shared(tfull_bar(slot0 + j), 1));
                         }
-                        // this chunk's product is complete in the TMEM of both CTAs
-                        tc_commit_pair(tfull_bar(slot0 + j));
-                        tc_commit_pair(mapa_shared(tfull_bar(slot0 + j), 1));
+                        __syncwarp();
                     }
                     if (!ok) break;
                     // the stage is reusable in both CTAs once these MMAs have read it
-                    tc_commit_pair(empty_bar(s));
-                    tc_commit_pair(mapa_shared(empty_bar(s), 1));
+                    if (elect_one()) {
+                        tc_commit_pair(empty_bar(s));
+                        tc_commit_pair(mapa_shared(empty_bar(s), 1));
+                    }
+                    __syncwarp();
                     const uint32_t parn = (((g + 2) >> 1) & 1u) ^ 1u;
 #pragma unroll
                     for (int j = 0; j < kUC; ++j) probe_t[j] = mbar_test_wait(tempty_bar(slot0 + j), parn) ? 1u : 0u;

@@ -172,7 +172,8 @@ fp8_gemm_tw_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsControl));
         if (warp == 0) {
             // ------------------------------------------------------------ TMA producer (both CTAs)
-            if (lane == 0) {
+            // (converged warp, elected lane: see the issuers)
+            {
                 uint32_t g = 0;
                 uint32_t probe = 0;   // result of test_wait on empty[] for chunk g, issued one chunk earlier
                 bool ok = true;
@@ -182,22 +183,25 @@ fp8_gemm_tw_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                     const int b_row = t.q * kBN + static_cast<int>(rank) * kBHalf;
                     for (int k = 0; k < kc; ++k, ++g) {
                         const int s = g % kStages;
-                        ok = wait_probed(probe, empty_bar(s), ((g / kStages) & 1u) ^ 1u, ctl, p.status, 1, g);
+                        ok = __all_sync(0xffffffffu, wait_probed(probe, empty_bar(s), ((g / kStages) & 1u) ^ 1u, ctl, p.status, 1, g));
                         if (!ok) break;
                         probe = mbar_test_wait(empty_bar((g + 1) % kStages), (((g + 1) / kStages) & 1u) ^ 1u) ? 1u : 0u;
                         const uint32_t lead_full = mapa_shared(full_bar(s), 0);
                         // the leader's barrier expects the bytes of both CTAs; the peer's loads may complete on it
                         // before this arrive has been made (the phase cannot complete without it)
-                        if (rank == 0) mbar_arrive_expect_tx(full_bar(s), 2 * kChunkBytes);
                         const uint32_t dst = tiles + s * kChunkBytes;
-                        tma_load_2d_pair(dst, &tmap_a, k * kChunk, a_row, lead_full);
-                        tma_load_2d_pair(dst + kPRows * kChunk, &tmap_b, k * kChunk, b_row, lead_full);
+                        if (elect_one()) {
+                            if (rank == 0) mbar_arrive_expect_tx(full_bar(s), 2 * kChunkBytes);
+                            tma_load_2d_pair(dst, &tmap_a, k * kChunk, a_row, lead_full);
+                            tma_load_2d_pair(dst + kPRows * kChunk, &tmap_b, k * kChunk, b_row, lead_full);
+                        }
+                        __syncwarp();
                     }
                 }
                 // Nothing waits for the commits onto the empty[] barriers of the last chunks; wait for them here so
                 // that none is in flight when the CTA leaves (it would land in whatever CTA gets this shared memory next).
                 for (uint32_t d = (g > kStages ? g - kStages : 0u); ok && d < g; ++d)
-                    ok = bounded_wait(empty_bar(d % kStages), (d / kStages) & 1u, ctl, p.status, 1, d);
+                    ok = __all_sync(0xffffffffu, bounded_wait(empty_bar(d % kStages), (d / kStages) & 1u, ctl, p.status, 1, d));
             }
         } else if (warp <= 2) {
             // ------------------------------------------------------------ MMA issuers (leader CTA; chunk g -> issuer g % 2)
