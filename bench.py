@@ -109,8 +109,8 @@ def gemm_bytes(M, N, K):
 # ncu captures of one launch each (commands and figures in the named summaries): measured DRAM bytes,
 # the (M, N, K) of the captured problem, the summary file.
 NCU_TRAFFIC = {
-    "token_major": (162.93e6 + 132.64e6, (4096, 18432, 7168), "profiles/fp8_gemm_tc_token_major_4096x18432x7168.md"),
-    "weight_major": (117.66e6 + 3.95e6, (8, 7168, 16384), "profiles/fp8_gemm_tc_weight_major_8x7168x16384.md"),
+    "token_major": (185.80e6 + 132.54e6, (4096, 18432, 7168), "profiles/fp8_gemm_tw_token_major_4096x18432x7168.md"),
+    "weight_major": (117.67e6 + 4.22e6, (8, 7168, 16384), "profiles/fp8_gemm_tc_weight_major_8x7168x16384.md"),
 }
 
 def read_peaks():
