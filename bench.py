@@ -280,7 +280,8 @@ def workload_config(world):
         "m_values": MS, "block_size": 128,
         "parallelism": "single GPU" if world == 1 else
                        f"tp{world}: the same problem set; column-parallel N/ws, row-parallel K/ws + NCCL all_reduce, "
-                       "replicated Linears on every rank (counted once), expert and TP=8-slice problems owned round-robin",
+                       "replicated Linears on every rank (counted once), expert and TP=8-slice problems owned round-robin; "
+                       "all_reduce on a communication stream, GEMMs leave it --comm-sms SMs while one is in flight",
         "l2": "inputs larger than L2: the sweep runs M-major, so >500 MB of other weights stream between two "
               "uses of any weight (L2 is 126 MB)",
     }
@@ -338,6 +339,7 @@ def run_ours(args):
     assert abs(total_flops - ref_flops) <= 1e-9 * ref_flops, (total_flops, ref_flops)
 
     comm = torch.cuda.Stream(device=dev) if world > 1 else None
+    sm_total = torch.cuda.get_device_properties(dev).multi_processor_count
 
     def column(M, collectives=True, with_act_quant=False):
         """fp8_gemm for every shape of the sweep at one M (one CUDA graph per column).  The all_reduce of a
@@ -345,14 +347,23 @@ def run_ours(args):
         joins the main stream at the end of the column, so it runs under the GEMMs that follow."""
         cur = torch.cuda.current_stream()
         pending = []
+        # While an all_reduce is (by estimate) in flight, the GEMMs leave it `--comm-sms` SMs: a persistent kernel on
+        # every SM keeps the collective's CTAs waiting until it ends, and the GEMM launched after that finds SMs
+        # taken and runs a straggling round.  t_gemm / t_comm_end: estimated device time since the column began.
+        t_gemm, t_comm_end, limited = 0.0, 0.0, False
         for name, K, N, _, ar, _c in rows:
             x, xq, xs = acts[K]
             wq, ws = weights[name]
+            want = collectives and args.comm_sms > 0 and t_gemm < t_comm_end
+            if want != limited:
+                dsv3_b200.set_num_sms(sm_total - args.comm_sms if want else 0)
+                limited = want
             if with_act_quant:
                 xq_m, xs_m = kernel.act_quant(x[:M])
                 y = kernel.fp8_gemm(xq_m, xs_m, wq, ws)
             else:
                 y = kernel.fp8_gemm(xq[:M], xs[:M], wq, ws)
+            t_gemm += gemm_flops(M, N, K) / 1.8e15 + 3e-6
             if ar and collectives:
                 ev = torch.cuda.Event()
                 ev.record(cur)
@@ -361,6 +372,10 @@ def run_ours(args):
                     dist.all_reduce(y)
                 y.record_stream(comm)
                 pending.append(y)
+                if M * N * 2 >= (4 << 20):
+                    t_comm_end = max(t_gemm, t_comm_end) + 2.0 * (world - 1) / world * (M * N * 2) / 550e9 + 20e-6
+        if limited:
+            dsv3_b200.set_num_sms(0)
         if pending:
             ev = torch.cuda.Event()
             ev.record(comm)
@@ -1177,6 +1192,8 @@ def run_decode_step(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--comm-sms", type=int, default=24,
+                    help="N > 1: SMs the GEMMs leave to an all_reduce that is in flight (0: none)")
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")

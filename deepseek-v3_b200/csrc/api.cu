@@ -35,16 +35,21 @@ int cuda_fail(cudaError_t e, const char* what) {
     return DSV3_ERR_CUDA;
 }
 
+static int g_sm_budget = 0;   // dsv3_set_num_sms: SMs the persistent GEMM kernels may occupy (0 = all)
+
 int num_sms() {
     static int cached[64] = {};
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-    if (cached[dev] == 0) {
-        int n = 0;
-        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-        cached[dev] = n;
+    int n = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64) {
+        if (cached[dev] == 0) {
+            int q = 0;
+            if (cudaDeviceGetAttribute(&q, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || q <= 0) q = 148;
+            cached[dev] = q;
+        }
+        n = cached[dev];
     }
-    return cached[dev];
+    return (g_sm_budget > 0 && g_sm_budget < n) ? g_sm_budget : n;
 }
 
 bool pdl_enabled() {
@@ -193,6 +198,15 @@ int dsv3_set_gemm_policy(int kernel, int split_k) {
     }
     g_force_kernel = kernel;
     g_force_split = split_k;
+    return DSV3_OK;
+}
+
+int dsv3_set_num_sms(int n) {
+    if (n < 0 || (n > 0 && n < 2)) {
+        set_last_error("set_num_sms: 0 (all SMs) or at least 2");
+        return DSV3_ERR_INVALID_ARGUMENT;
+    }
+    g_sm_budget = n;
     return DSV3_OK;
 }
 

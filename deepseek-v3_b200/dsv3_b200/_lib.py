@@ -26,7 +26,7 @@ EXPORTS = (
     "dsv3_check_device_status", "dsv3_fp8_gemm_static", "dsv3_fp8_gemm_static_scratch_bytes",
     "dsv3_group_table_bytes", "dsv3_group_table_build", "dsv3_fp8_gemm_grouped", "dsv3_moe_combine", "dsv3_moe_route",
     "dsv3_fp8_linear", "dsv3_swiglu_quant", "dsv3_selftest_bounded_wait", "dsv3_p2p_handle_bytes", "dsv3_p2p_create", "dsv3_p2p_connect", "dsv3_p2p_connect_local", "dsv3_p2p_base",
-    "dsv3_allreduce_oneshot", "dsv3_allreduce_oneshot_pair_on_one_gpu", "dsv3_p2p_destroy",
+    "dsv3_allreduce_oneshot", "dsv3_allreduce_oneshot_pair_on_one_gpu", "dsv3_p2p_destroy", "dsv3_set_num_sms",
 )
 
 
@@ -80,6 +80,8 @@ def _load() -> ctypes.CDLL:
     lib.dsv3_moe_route.argtypes = [vp, vp, i64, ci, ci, ci, vp, vp, vp, vp, vp, vp]
     lib.dsv3_moe_route.restype = ci
     lib.dsv3_set_gemm_policy.argtypes = [ci, ci]
+    lib.dsv3_set_num_sms.argtypes = [ci]
+    lib.dsv3_set_num_sms.restype = ci
     lib.dsv3_weight_quant.argtypes = [vp, i64, i64, vp, vp, vp]
     lib.dsv3_check_device_status.argtypes = [vp, ctypes.POINTER(ctypes.c_uint32 * 4)]
     for name in ("dsv3_act_quant", "dsv3_weight_dequant", "dsv3_fp8_gemm", "dsv3_set_gemm_policy",

@@ -230,6 +230,11 @@ def set_gemm_policy(kernel: int = KERNEL_AUTO, split_k: int = 0) -> None:
     _lib.check(lib.dsv3_set_gemm_policy(kernel, split_k))
 
 
+def set_num_sms(n: int = 0) -> None:
+    """SMs the persistent GEMM kernels may occupy from now on (0 = all): leave a concurrent collective its SMs."""
+    _lib.check(lib.dsv3_set_num_sms(int(n)))
+
+
 def check_device_status() -> None:
     """Synchronise the current stream and raise if a kernel's bounded wait gave up."""
     import ctypes

@@ -147,6 +147,16 @@ int dsv3_fp8_gemm_static(const void* a, const float* a_s, const void* b, const f
 int dsv3_set_gemm_policy(int kernel, int split_k);
 
 /*
+ * SMs the persistent tcgen05 GEMM kernels (and the plans that size split-K for them) may occupy; 0 = all
+ * (default).  No counterpart in the reference.  For hosts that run a collective next to the GEMMs: a persistent
+ * kernel that fills every SM keeps the collective's CTAs waiting until it ends, and the GEMM launched after that
+ * finds SMs taken and runs a straggling round; leaving the collective its SMs (about as many as it has
+ * channels) avoids both.  Process-wide like the policy above: read when a GEMM is launched (or captured), so it can
+ * be changed between the launches of one captured graph; change it only while no other thread is inside the library.
+ */
+int dsv3_set_num_sms(int n);
+
+/*
  * Grouped fp8_gemm over per-expert weights -- replaces the expert loop of MoE.forward
  * (model.py:683-689: one act_quant + fp8_gemm triple per expert and two host synchronisations per
  * expert) by one launch per projection.

@@ -337,3 +337,24 @@ def test_bounded_wait_gives_up_and_reports_through_the_status_words():
     dsv3_b200.check_device_status()          # clean again
     with pytest.raises(_lib.Dsv3Error):
         _lib.check(_lib.lib.dsv3_selftest_bounded_wait(0, st))
+
+
+@pytest.mark.parametrize("M,N,Kd,seed", [(1024, 4096, 1024, 70), (640, 4616, 896, 71), (16, 4096, 2048, 72)])
+def test_fp8_gemm_on_an_sm_budget_is_bit_identical(K, M, N, Kd, seed):
+    """dsv3_set_num_sms: the persistent kernels on fewer SMs (a host leaving room for a collective) walk the same
+    tiles in another distribution; results do not change."""
+    import dsv3_b200
+    xq, xs, wq, ws = quantised_case(M, N, Kd, seed)
+    y = run(K, AUTO, 0, xq, xs, wq, ws)
+    try:
+        for budget in (100, 16, 2):
+            dsv3_b200.set_num_sms(budget)
+            if M <= 64:      # split-K plans depend on the SM count (the token-major shapes here have more tiles than
+                             # SMs and never split): compare within the tolerance, not bit for bit
+                assert_gemm_close(run(K, AUTO, 0, xq, xs, wq, ws), O.fp8_gemm(xq, xs, wq, ws))
+            else:
+                assert np.array_equal(bf16_bits(run(K, AUTO, 0, xq, xs, wq, ws)), bf16_bits(y)), budget
+        with pytest.raises(dsv3_b200.Dsv3Error):
+            dsv3_b200.set_num_sms(1)
+    finally:
+        dsv3_b200.set_num_sms(0)
