@@ -212,7 +212,7 @@ int dsv3_set_num_sms(int n) {
 
 size_t dsv3_fp8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K) {
     if (M <= 0 || N <= 0 || K <= 0 || g_force_kernel == 1 || g_force_kernel == 5 || (K % 16) != 0) return 0;
-    if (g_force_kernel == 0 && g_force_split == 0 && M <= 8 && N >= 2048 && N * K <= (6ll << 20)) return 0;   // decode kernel
+    if (g_force_kernel == 0 && g_force_split == 0 && M <= 8 && N >= 2048 && K >= 1024 && N * K <= (6ll << 20)) return 0;   // decode kernel
     const TcPlan pl = tc_plan(M, N, K, g_force_kernel, g_force_split);
     if (pl.error != DSV3_OK) return 0;     // dsv3_fp8_gemm reports the reason
     return tc_workspace_bytes(pl, M, N);
@@ -241,10 +241,11 @@ int dsv3_fp8_gemm(const void* a, const float* a_s, const void* b, const float* b
         }
         return launch_fp8_linear_small(nullptr, a, a_s, b, b_s, M, N, K, DSV3_SCALE_FMT_FP32, c, st);
     }
-    // Automatic choice, decode-sized problems with a few megabytes of weights in many rows: the register-streaming
-    // kernel has less to set up than the tcgen05 pipeline (measured on B200 at M = 1..8: N 3072 x K 1536: 4.5-4.8 vs
-    // 5.9-6.0 us; N 4096 x K 512: 3.4 vs 3.8 us; at 11 MB and more the two are level or the tcgen05 kernel is ahead).
-    if (g_force_kernel == 0 && g_force_split == 0 && M <= 8 && N >= 2048 && N * K <= (6ll << 20) &&
+    // Automatic choice, decode-sized problems with a few megabytes of weights in many rows and at least eight K
+    // chunks: the register-streaming kernel has less to set up than the tcgen05 pipeline (measured on B200 at
+    // M = 1..8: N 3072 x K 1536: 4.5-4.6 vs 4.8-4.9 us; with shorter K the tcgen05 kernel is level or ahead -- N 4096 x
+    // K 512: 3.2 vs 3.2 us, N 7168 x K 256: 3.3-3.6 vs 2.9-3.0 us -- as it is at 11 MB and more: 7.4 vs 6.1 us).
+    if (g_force_kernel == 0 && g_force_split == 0 && M <= 8 && N >= 2048 && K >= 1024 && N * K <= (6ll << 20) &&
         small_linear_supported(a, b, c, M, N, K, false))
         return launch_fp8_linear_small(nullptr, a, a_s, b, b_s, M, N, K, DSV3_SCALE_FMT_FP32, c, st);
     const bool tc_ok = tc_supported(a, b, c, M, N, K);

@@ -239,8 +239,12 @@ __global__ void __launch_bounds__(kThreads) fp8_linear_small_kernel(const SmallP
                 st_cluster_f32(base + 4u * static_cast<uint32_t>(((slot * WR + wr) * 16 + row) * TOK + tok), acc[j][i]);
             }
     }
-    cluster_arrive();
-    cluster_wait();
+    if (p.csize > 1) {
+        cluster_arrive();
+        cluster_wait();
+    } else {
+        __syncthreads();      // launched without a cluster: the slots are this CTA's own
+    }
     if (rank == 0) {
         const int n_slots = p.csize * WK;
         constexpr int ROWS = WR * 16;
@@ -274,15 +278,24 @@ int launch_variant(const SmallParams& prm, int rowgroups, size_t smem_bytes, cud
     cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = smem_bytes;
     cfg.stream = stream;
+    // attributes: dependent launch first, the cluster dimension only when K is split over more than one CTA (a
+    // cluster launch, even of one CTA, takes a slower path through the launch machinery)
     cudaLaunchAttribute attr[2];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = static_cast<unsigned>(prm.csize);
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    int n_attr = 0;
+    if (pdl_enabled()) {
+        attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+        ++n_attr;
+    }
+    if (prm.csize > 1) {
+        attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+        attr[n_attr].val.clusterDim.x = static_cast<unsigned>(prm.csize);
+        attr[n_attr].val.clusterDim.y = 1;
+        attr[n_attr].val.clusterDim.z = 1;
+        ++n_attr;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    cfg.numAttrs = n_attr;
     DSV3_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, prm));
     return DSV3_OK;
 }
