@@ -338,7 +338,9 @@ def run_ours(args):
     ref_flops = sum(gemm_flops(M, N, K) for M in MS for (_, K, N, *_r) in sweep_rows(1))
     assert abs(total_flops - ref_flops) <= 1e-9 * ref_flops, (total_flops, ref_flops)
 
-    comm = torch.cuda.Stream(device=dev) if world > 1 else None
+    # high priority: when SMs come free, the collective's CTAs go ahead of the next GEMM's (already queued under
+    # programmatic dependent launch)
+    comm = torch.cuda.Stream(device=dev, priority=-1) if world > 1 else None
     sm_total = torch.cuda.get_device_properties(dev).multi_processor_count
 
     def column(M, collectives=True, with_act_quant=False):
