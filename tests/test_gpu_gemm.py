@@ -108,6 +108,7 @@ PAIR = [  # shapes for the CTA-pair kernels: (M, N, K, seed)
     (129, 128, 128, 60),      # second CTA of the only pair has one valid token row; a single K chunk
     (129, 129, 128, 66),      # 256-wide tiles: one valid column in the right half
     (513, 2052, 640, 67),     # 256-wide tiles: the last tile's right half lies wholly beyond N
+    (384, 640, 448, 68),      # K tail: the last chunk is half zero fill (K % 128 = 64), three token tiles
     (300, 520, 896, 61),      # odd number of token tiles (the last pair's second tile is empty), odd number of K chunks
     (256, 1000, 1152, 62),    # N % 8 != 0 would forbid the tensor-map store: 1000 is fine, see next
     (257, 1001, 384, 63),     # N % 8 != 0: plain stores; three token tiles
