@@ -51,6 +51,37 @@ def test_argument_validation_without_gpu():
     assert L.dsv3_set_gemm_policy(0, 0) == _lib.OK
 
 
+def test_plan_and_setters_without_gpu():
+    """Host-side planning: the workspace query is pure arithmetic over the shape, the policy and the SM budget."""
+    from dsv3_b200 import _lib
+    L = _lib.lib
+    ws = L.dsv3_fp8_gemm_workspace_bytes
+    try:
+        assert L.dsv3_set_num_sms(1) == _lib.ERR_INVALID_ARGUMENT and L.dsv3_set_num_sms(-3) == _lib.ERR_INVALID_ARGUMENT
+        assert L.dsv3_set_num_sms(0) == _lib.OK
+        # prefill-sized problems with more tiles than SMs never split K: no workspace, whichever pair kernel is chosen
+        assert ws(4096, 18432, 7168) == 0 and ws(16384, 7168, 2048) == 0 and ws(4096, 1536, 7168) == 0
+        # a decode problem with few weight tiles and long K splits K: ticket header + padded partial tiles
+        need = ws(8, 7168, 16384)
+        assert need > _lib.WORKSPACE_HEADER_BYTES and (need - _lib.WORKSPACE_HEADER_BYTES) % (128 * 16 * 4) == 0
+        # pinned kernels that never split ask for nothing; a pinned split factor is reflected in the size
+        for policy in (1, 4, 5, 6):
+            assert L.dsv3_set_gemm_policy(policy, 0) == _lib.OK
+            assert ws(4096, 7168, 2048) == 0
+        assert L.dsv3_set_gemm_policy(3, 4) == _lib.OK
+        tiles = -(-7168 // 128)
+        assert ws(8, 7168, 16384) == _lib.WORKSPACE_HEADER_BYTES + 4 * tiles * 128 * 16 * 4
+        # an SM budget changes the plan of a problem that filled the machine before
+        assert L.dsv3_set_gemm_policy(0, 0) == _lib.OK
+        full = ws(32, 18432, 7168)
+        assert L.dsv3_set_num_sms(32) == _lib.OK
+        small = ws(32, 18432, 7168)
+        assert small <= full
+    finally:
+        L.dsv3_set_gemm_policy(0, 0)
+        L.dsv3_set_num_sms(0)
+
+
 def test_shim_signatures_match_reference():
     import inspect
     import kernel
