@@ -1048,7 +1048,7 @@ def run_decode_step(args):
     oneshot = {"ar": None, "on": False}
     if world > 1:
         try:
-            oneshot["ar"] = dsv3_b200.P2PAllReduce(max_bytes=1 << 20)
+            oneshot["ar"] = dsv3_b200.P2PAllReduce(max_bytes=256 << 10)   # larger messages stay on NCCL
         except Exception as e:      # no peer access between the ranks' GPUs: NCCL only
             sys.stderr.write(f"one-shot all-reduce unavailable: {e}\n")
 
